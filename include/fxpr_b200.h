@@ -1,0 +1,165 @@
+/*
+ * fxpr_b200 -- C ABI of the B200 (sm_100a) fixed-point reduction kernels.
+ *
+ * Every entry point takes raw DEVICE pointers, plain sizes/strides, the Q-format
+ * and a CUDA stream (a cudaStream_t passed as void*), launches on that stream,
+ * never synchronises, never allocates (unless its comment says so) and returns
+ * FXPR_OK or a negative status.  The library owns no memory: outputs and scratch
+ * are the caller's (in the Python host layer they are torch tensors, so the
+ * caching allocator and CUDA-graph capture keep working).
+ *
+ * Each entry replaces one launcher of the reference plugin fxpr_vllm (a pure
+ * Python/Triton project, so the "FFI" it replaces is the Python call of a
+ * `*_run` launcher from fxpr_vllm/_lib.py); the file:line beside each
+ * declaration names that launcher.
+ */
+#ifndef FXPR_B200_H_
+#define FXPR_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------ */
+#define FXPR_OK               0
+#define FXPR_ERR_BAD_ARG     -1  /* null pointer, negative size, bad bit width    -> ValueError   */
+#define FXPR_ERR_UNSUPPORTED -2  /* dtype / layout not implemented                -> TypeError    */
+#define FXPR_ERR_SCRATCH     -3  /* scratch buffer missing or too small           -> RuntimeError */
+#define FXPR_ERR_CUDA        -4  /* a CUDA runtime/driver call failed             -> RuntimeError */
+#define FXPR_ERR_TIMEOUT     -5  /* a bounded device-side wait gave up            -> RuntimeError */
+#define FXPR_ERR_ARCH        -6  /* device is not compute capability 10.x         -> RuntimeError */
+
+/* ---- element types ----------------------------------------------------- */
+#define FXPR_F16  0
+#define FXPR_BF16 1
+#define FXPR_F32  2
+#define FXPR_F64  3
+
+/* ---- gemm flags -------------------------------------------------------- */
+#define FXPR_GEMM_FORCE_PORTABLE 1  /* route to the CUDA-core kernel (sequential-k partials) */
+
+/* ---- attention flags --------------------------------------------------- */
+#define FXPR_ATTN_CAUSAL         1
+#define FXPR_ATTN_FORCE_PORTABLE 2  /* route to the CUDA-core kernel (sequential partials) */
+
+int fxpr_version(void);
+const char* fxpr_status_string(int status);
+
+/* Last CUDA error text recorded by this library on the calling thread ("" if none). */
+const char* fxpr_last_error(void);
+
+/*
+ * y[i] = saturate(rint_half_even(fp32(x[i]) * 2^frac_bits)) as int{16,32,64}.
+ * x_dtype in {FXPR_F16, FXPR_F32, FXPR_F64}; n elements, both contiguous.
+ * Replaces float_to_fixed_run, fxpr_vllm/_triton/casts.py:57-89
+ * (device math fxpr_vllm/_triton/fxp.py:92-108).
+ */
+int fxpr_float_to_fixed(const void* x, int x_dtype, void* y, int int_bits,
+                        int frac_bits, int64_t n, void* stream);
+
+/*
+ * y[i] = T(fp32(x[i]) * 2^-frac_bits), x int{16,32,64}, T = fp{16,32,64}.
+ * Replaces fixed_to_float_run, fxpr_vllm/_triton/casts.py:92-126.
+ */
+int fxpr_fixed_to_float(const void* x, int int_bits, void* y, int float_bits,
+                        int frac_bits, int64_t n, void* stream);
+
+/*
+ * RMSNorm over rows of a contiguous [rows, hidden] matrix, optional fused
+ * residual add (residual != NULL: residual <- T(x + residual) in place, and the
+ * rounded sum is what gets normalised).  The sum of squares is an int64 sum of
+ * Q(frac_bits) integers; mean, 1/sqrt and the scaling are single IEEE
+ * operations.  dtype in {FXPR_F16, FXPR_BF16, FXPR_F32}; weight has that dtype.
+ * Replaces _common_launch, fxpr_vllm/_triton/rms_norm.py:78-134 (whose kernel
+ * sums in fp32, rms_norm.py:38-50).
+ */
+int fxpr_rms_norm(const void* x, void* residual, const void* weight, void* y,
+                  int dtype, int64_t rows, int64_t hidden, float eps,
+                  int frac_bits, void* stream);
+
+/*
+ * Row-wise log-softmax of a contiguous [rows, cols] matrix into fp32:
+ * y = (x - max) - log(sum_int64(Q(exp(x - max)))).  x_dtype in
+ * {FXPR_F16, FXPR_BF16, FXPR_F32}.  No counterpart in the reference (the
+ * sampler files its README lists are absent); hook point is vLLM's
+ * Sampler.compute_logprobs.
+ */
+int fxpr_log_softmax(const void* x, int x_dtype, float* y, int64_t rows,
+                     int64_t cols, int frac_bits, void* stream);
+
+/*
+ * Bytes of zero-initialised scratch fxpr_gemm needs for this problem
+ * (0 when split_k <= 1).  The kernel leaves the scratch zeroed again.
+ * Replaces _get_splitk_scratch, fxpr_vllm/_triton/gemm.py:86-107.
+ */
+int64_t fxpr_gemm_scratch_bytes(int64_t M, int64_t N, int int_bits, int split_k);
+
+/*
+ * C[M,N] = T( fp32( sum_t Q( fp32dot(A[:, tile t], B[tile t, :]) ) ) * 2^-frac + bias ).
+ * a: (M,K) element strides a_sm,a_sk.  b: (K,N) strides b_sk,b_sn.  c: (M,N)
+ * row stride c_sm, unit column stride; may be NULL when only c_int is wanted.
+ * c_int: optional contiguous [M,N] int{int_bits} receiving the integer
+ * accumulators (for the tensor-parallel reduce and for tests).
+ * k_tile: conversion granularity (0 = reference default: 128 for f16/bf16, 64
+ * for f32).  split_k: 0/1 = none, else the K-tiles are dealt round-robin to
+ * split_k CTAs per output tile and merged with integer atomics (needs scratch).
+ * partials_out: optional fp32 [ceil(K/k_tile), M, N] dump of the per-tile
+ * float partials (tests only; must be NULL when split_k > 1).
+ * Replaces gemm_fxp_run, fxpr_vllm/_triton/gemm.py:612-763.
+ */
+int fxpr_gemm(const void* a, const void* b, const void* bias, void* c, void* c_int,
+              int dtype, int64_t M, int64_t N, int64_t K,
+              int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, int64_t c_sm,
+              int int_bits, int frac_bits, int k_tile, int split_k, int flags,
+              void* scratch, int64_t scratch_bytes, float* partials_out,
+              void* stream);
+
+/*
+ * c = T(fp32(c_int) * 2^-frac + bias): the GEMM epilogue applied to integer
+ * accumulators that were summed across tensor-parallel ranks.  c_int is a
+ * contiguous [M,N] int{int_bits}.  Same formula as gemm.py:195-204.
+ */
+int fxpr_gemm_epilogue_from_int(const void* c_int, int int_bits, const void* bias,
+                                void* c, int dtype, int64_t M, int64_t N,
+                                int64_t c_sm, int frac_bits, void* stream);
+
+/*
+ * Bytes of scratch fxpr_attention needs (any contents; the call initialises
+ * what it uses).  Replaces the per-call torch.full/zeros of
+ * fxpr_vllm/_triton/attention.py:838-851.
+ */
+int64_t fxpr_attention_scratch_bytes(int64_t total_q_tokens, int num_heads,
+                                     int head_dim, int int_bits, int num_splits);
+
+/*
+ * Unified prefill + decode attention over a paged KV cache with integer
+ * softmax denominator and P.V numerator.
+ * q,o: [T, Hq, D] (token/head strides in elements, unit stride in D).
+ * kv_cache: [num_blocks, 2, page, Hkv, D] given as separate K and V base
+ * pointers plus block/slot/head strides (elements).  query_start_loc [R+1],
+ * seq_lens [R], block_table [R, bt_stride] int32.  alibi: fp32 [Hq] slopes
+ * already multiplied by log2(e), or NULL.  softmax_scale is the plain scale
+ * (the call multiplies by log2(e)).  logit_softcap 0 = off, window 0 = off.
+ * num_splits >= 1 (the host picks it).  status_word: optional device int set
+ * non-zero by a kernel that gave up on a bounded wait.
+ * Replaces unified_attention_fxp_run, fxpr_vllm/_triton/attention.py:692-953.
+ */
+int fxpr_attention(const void* q, const void* k_cache, const void* v_cache, void* o,
+                   const int32_t* query_start_loc, const int32_t* seq_lens,
+                   const int32_t* block_table, const float* alibi,
+                   int dtype, int64_t total_q_tokens, int num_reqs, int num_heads,
+                   int num_kv_heads, int head_dim, int page_size,
+                   int64_t q_st, int64_t q_sh, int64_t o_st, int64_t o_sh,
+                   int64_t kv_sblock, int64_t kv_sslot, int64_t kv_shead,
+                   int64_t bt_stride, int max_query_len, int flags,
+                   double softmax_scale, double logit_softcap, int window,
+                   int int_bits, int frac_bits, int num_splits,
+                   void* scratch, int64_t scratch_bytes, int32_t* status_word,
+                   void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FXPR_B200_H_ */

@@ -1,0 +1,185 @@
+"""GPU parity of the unified paged attention.
+
+* CUDA-core route: bit-exact against the CPU oracle.
+* default route: within tolerance of the oracle / float softmax, and bitwise
+  invariant to the KV split count, repeats and batching (decode row == the same
+  row computed inside a prefill chunk).
+* the reference's tests (fxpr_vllm/_tests/test_decode.py, test_prefill.py)
+  re-stated, including its page_size=1 adapter.
+"""
+from __future__ import annotations
+
+import math
+
+import pytest
+import torch
+
+import fxpr_vllm  # noqa: F401
+from fxpr_vllm import _lib as L
+from oracle import fxp_oracle as orc
+
+pytestmark = pytest.mark.gpu
+_DTYPES = [torch.float16, torch.bfloat16, torch.float32]
+
+
+def _h():
+    import fxp_helpers
+    return fxp_helpers
+
+
+def _mixed_batch(dtype, hq, hkv, d, page, seed, ctx=(37, 150, 70), qlens=(1, 5, 70)):
+    g = torch.Generator().manual_seed(seed)
+    seq = list(ctx)  # seq_lens count the new tokens too
+    kv, bt = _h().make_paged_kv(seq, hkv, d, page, dtype, g)
+    qsl = torch.tensor([0] + list(torch.tensor(qlens).cumsum(0)), dtype=torch.int32)
+    q = torch.randn((int(qsl[-1]), hq, d), generator=g).to(dtype)
+    return q.cuda(), kv, qsl.cuda(), torch.tensor(seq, dtype=torch.int32).cuda(), bt, max(qlens)
+
+
+@pytest.mark.parametrize("dtype", _DTYPES)
+@pytest.mark.parametrize("hq,hkv,d,page", [(4, 2, 32, 16), (4, 1, 80, 16), (2, 2, 64, 1)])
+@pytest.mark.parametrize("splits", [1, 3])
+@pytest.mark.parametrize("int_bits", [32, 64])
+def test_portable_bit_exact(dtype, hq, hkv, d, page, splits, int_bits):
+    q, kv, qsl, sl, bt, mq = _mixed_batch(dtype, hq, hkv, d, page, 7)
+    with L.overrides(attn_portable=True):
+        got = _h().run_attention(q, kv, qsl, sl, bt, mq, int_bits=int_bits, splits=splits).cpu()
+    exp = orc.attention_fxp(q.cpu(), kv.cpu(), qsl.cpu(), sl.cpu(), bt.cpu(), int_bits=int_bits)
+    assert torch.equal(got.view(torch.uint8), exp.view(torch.uint8))
+
+
+@pytest.mark.parametrize("kwargs", [dict(causal=False), dict(window=24), dict(alibi=True),
+                                    dict(scale=0.05), dict(frac_bits=8)])
+def test_portable_flags_bit_exact(kwargs):
+    dtype = torch.bfloat16
+    q, kv, qsl, sl, bt, mq = _mixed_batch(dtype, 4, 2, 32, 16, 9)
+    kw = dict(kwargs)
+    alibi = None
+    if kw.pop("alibi", False):
+        alibi = torch.tensor([0.1, 0.2, 0.3, 0.4]) * orc.RCP_LN2
+    with L.overrides(attn_portable=True):
+        got = _h().run_attention(q, kv, qsl, sl, bt, mq, splits=2,
+                                 alibi=None if alibi is None else alibi.cuda(), **kw).cpu()
+    exp = orc.attention_fxp(q.cpu(), kv.cpu(), qsl.cpu(), sl.cpu(), bt.cpu(),
+                            alibi_slopes=alibi, is_causal=kw.get("causal", True),
+                            softmax_scale=kw.get("scale"), frac_bits=kw.get("frac_bits", 16),
+                            window_size=kw.get("window", 0))
+    assert torch.equal(got.view(torch.uint8), exp.view(torch.uint8))
+
+
+def _float_attention(q, kv, qsl, sl, bt, causal=True, softcap=0.0):
+    q, kv = q.float().cpu(), kv.float().cpu()
+    out = torch.zeros_like(q)
+    page, hkv = kv.shape[2], kv.shape[3]
+    hq, d = q.shape[1], q.shape[2]
+    for r in range(sl.numel()):
+        s = int(sl[r]); q0, q1 = int(qsl[r]), int(qsl[r + 1])
+        pos = torch.arange(s)
+        k = kv[bt[r, pos // page].long().cpu(), 0, pos % page]
+        v = kv[bt[r, pos // page].long().cpu(), 1, pos % page]
+        rows = s - (q1 - q0) + torch.arange(q1 - q0)
+        for h in range(hq):
+            sc = (q[q0:q1, h] @ k[:, h // (hq // hkv)].T) / math.sqrt(d)
+            if softcap > 0:
+                sc = softcap * torch.tanh(sc / softcap)
+            if causal:
+                sc = sc.masked_fill(pos[None, :] > rows[:, None], float("-inf"))
+            out[q0:q1, h] = torch.softmax(sc, -1) @ v[:, h // (hq // hkv)]
+    return out
+
+
+@pytest.mark.parametrize("dtype", _DTYPES)
+@pytest.mark.parametrize("hq,hkv,d,page", [(4, 2, 32, 16), (32, 8, 128, 16), (8, 8, 64, 32)])
+@pytest.mark.parametrize("causal", [True, False])
+def test_default_route_vs_float_softmax(dtype, hq, hkv, d, page, causal):
+    q, kv, qsl, sl, bt, mq = _mixed_batch(dtype, hq, hkv, d, page, 11, ctx=(200, 64, 129),
+                                          qlens=(1, 64, 33))
+    got = _h().run_attention(q, kv, qsl, sl, bt, mq, causal=causal).float().cpu()
+    ref = _float_attention(q, kv, qsl, sl, bt, causal)
+    assert torch.allclose(got, ref, atol=5e-2, rtol=5e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_default_route_close_to_oracle(dtype):
+    q, kv, qsl, sl, bt, mq = _mixed_batch(dtype, 8, 2, 128, 16, 13, ctx=(300, 90), qlens=(1, 40))
+    got = _h().run_attention(q, kv, qsl, sl, bt, mq, int_bits=64).float().cpu()
+    exp = orc.attention_fxp(q.cpu(), kv.cpu(), qsl.cpu(), sl.cpu(), bt.cpu(), int_bits=64,
+                            sequential=False, exp2_fn=torch.exp2).float()
+    # outputs agree to one rounding step of the IO dtype plus a couple of Q16.16 LSB
+    tol = 2.0 ** -7 if dtype == torch.bfloat16 else 2.0 ** -9
+    assert (got - exp).abs().max().item() <= tol
+
+
+@pytest.mark.parametrize("dtype", _DTYPES)
+@pytest.mark.parametrize("hq,hkv,d,page", [(4, 2, 32, 16), (32, 8, 128, 16)])
+@pytest.mark.parametrize("int_bits", [32, 64])
+def test_split_and_repeat_invariance(dtype, hq, hkv, d, page, int_bits):
+    q, kv, qsl, sl, bt, mq = _mixed_batch(dtype, hq, hkv, d, page, 17, ctx=(160, 96, 700),
+                                          qlens=(1, 1, 1))
+    ref = _h().run_attention(q, kv, qsl, sl, bt, 1, int_bits=int_bits, splits=1)
+    for splits in (1, 2, 4, 8, 16):
+        for _ in range(2):
+            got = _h().run_attention(q, kv, qsl, sl, bt, 1, int_bits=int_bits, splits=splits)
+            assert torch.equal(ref, got), f"splits={splits}"
+
+
+@pytest.mark.parametrize("dtype", _DTYPES)
+def test_prefill_split_invariance_and_auto_policy(dtype):
+    q, kv, qsl, sl, bt, mq = _mixed_batch(dtype, 4, 2, 64, 16, 19, ctx=(130, 257), qlens=(130, 257))
+    ref = _h().run_attention(q, kv, qsl, sl, bt, mq, splits=1)
+    for splits in (0, 2, 4, 8):
+        assert torch.equal(ref, _h().run_attention(q, kv, qsl, sl, bt, mq, splits=splits))
+
+
+@pytest.mark.parametrize("dtype", _DTYPES)
+@pytest.mark.parametrize("hq,hkv,d", [(4, 2, 32), (32, 8, 128)])
+def test_decode_row_equals_prefill_row(dtype, hq, hkv, d):
+    """Batch invariance across kernel variants: the last token of a prefill chunk
+    and the same token issued as a decode step give identical bits."""
+    g = torch.Generator().manual_seed(23)
+    s = 173
+    kv, bt = _h().make_paged_kv([s], hkv, d, 16, dtype, g)
+    q = torch.randn((s, hq, d), generator=g).to(dtype).cuda()
+    sl = torch.tensor([s], dtype=torch.int32).cuda()
+    full = _h().run_attention(q, kv, torch.tensor([0, s], dtype=torch.int32).cuda(), sl, bt, s)
+    chunk = _h().run_attention(q[-40:].contiguous(), kv, torch.tensor([0, 40], dtype=torch.int32).cuda(), sl, bt, 40)
+    dec = _h().run_attention(q[-1:].contiguous(), kv, torch.tensor([0, 1], dtype=torch.int32).cuda(), sl, bt, 1)
+    assert torch.equal(full[-1], dec[0]) and torch.equal(full[-40:], chunk)
+
+
+def test_key_tile_permutation_invariance_page1():
+    """Reference's test_prefill.py:246-279 idea: permuting whole 64-key tiles of a
+    non-causal problem leaves the output bits unchanged."""
+    dtype, hq, d, n = torch.bfloat16, 2, 32, 256
+    g = torch.Generator().manual_seed(29)
+    q = torch.randn((n, hq, d), generator=g).to(dtype).cuda()
+    k = torch.randn((n, hq, d), generator=g).to(dtype)
+    v = torch.randn((n, hq, d), generator=g).to(dtype)
+
+    def run(kk, vv):
+        kv = torch.stack([kk, vv], dim=1).unsqueeze(2).contiguous().cuda()  # page_size 1
+        bt = torch.arange(n, dtype=torch.int32).reshape(1, n).cuda()
+        return _h().run_attention(q, kv, torch.tensor([0, n], dtype=torch.int32).cuda(),
+                                  torch.tensor([n], dtype=torch.int32).cuda(), bt, n, causal=False)
+
+    tperm = torch.randperm(4, generator=g)
+    idx = torch.cat([torch.arange(t * 64, (t + 1) * 64) for t in tperm])
+    assert torch.equal(run(k, v), run(k[idx], v[idx]))
+
+
+def test_softcap_and_errors():
+    q, kv, qsl, sl, bt, mq = _mixed_batch(torch.bfloat16, 4, 2, 32, 16, 31)
+    got = _h().run_attention(q, kv, qsl, sl, bt, mq, softcap=20.0).float().cpu()
+    ref = _float_attention(q, kv, qsl, sl, bt, True, softcap=20.0)
+    assert torch.allclose(got, ref, atol=5e-2, rtol=5e-2)
+    o = torch.empty_like(q)
+    with pytest.raises(TypeError):
+        torch.ops.fxpr.unified_attention_fxp(q, kv, o, qsl.long(), sl, bt, mq, None, True, None, 32, 16, 0.0, 0, 1)
+    with pytest.raises(ValueError):
+        torch.ops.fxpr.unified_attention_fxp(q, kv[:, :1], o, qsl, sl, bt, mq, None, True, None, 32, 16, 0.0, 0, 1)
+    with pytest.raises(ValueError):
+        torch.ops.fxpr.unified_attention_fxp(q, kv, o, qsl, sl, bt, mq, None, True, None, 32, 16, 0.0, 0, -1)
+    with pytest.raises(TypeError):
+        torch.ops.fxpr.unified_attention_fxp(q, kv.float(), o, qsl, sl, bt, mq, None, True, None, 32, 16, 0.0, 0, 1)
+    # empty batch is a no-op
+    torch.ops.fxpr.unified_attention_fxp(q[:0], kv, o[:0], qsl[:1], sl[:0], bt[:0], 0, None, True, None, 32, 16, 0.0, 0, 1)

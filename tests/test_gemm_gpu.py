@@ -1,0 +1,203 @@
+"""GPU parity of the fixed-point GEMM.
+
+* CUDA-core route: bit-exact against the CPU oracle (same ascending-k order).
+* tensor-core route: integer stage bit-exact given the kernel's own fp32
+  partials; end to end within a few Q-format LSB of the oracle (different
+  in-tile summation order); bitwise invariant to split-K, batch size, K-tile
+  order and repeats.
+* the reference's own tests (fxpr_vllm/_tests/test_gemm.py) re-stated.
+"""
+from __future__ import annotations
+
+import pytest
+import torch
+
+import fxpr_vllm  # noqa: F401
+from fxpr_vllm import _lib as L
+from oracle import fxp_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+_TOL = {torch.float32: (5e-4, 5e-4), torch.float16: (1e-2, 1e-2), torch.bfloat16: (5e-2, 5e-2)}
+_DTYPES = [torch.float32, torch.float16, torch.bfloat16]
+
+
+def _gemm(a, b, bias=None, int_bits=32, frac_bits=16):
+    return torch.ops.fxpr.gemm_fxp(a, b, bias, int_bits, frac_bits)
+
+
+def _rand(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype)
+
+
+# ---------------- CUDA-core route: bit-exact vs oracle -----------------------------
+
+@pytest.mark.parametrize("dtype", _DTYPES)
+@pytest.mark.parametrize("M,N,K", [(1, 1, 32), (3, 7, 16), (4, 4, 33), (130, 130, 33), (65, 200, 300)])
+@pytest.mark.parametrize("int_bits", [16, 32, 64])
+def test_portable_bit_exact(dtype, M, N, K, int_bits):
+    a = _rand((M, K), dtype, 1, 0.5)
+    b = _rand((K, N), dtype, 2, 0.5)
+    bias = _rand((N,), dtype, 3)
+    with L.overrides(gemm_portable=True):
+        got = _gemm(a.cuda(), b.cuda(), bias.cuda(), int_bits, 16).cpu()
+        got_int = torch.ops.fxpr.gemm_fxp_int(a.cuda(), b.cuda(), int_bits, 16).cpu()
+    exp_int = orc.gemm_fxp(a, b, None, int_bits, 16, sequential=True, return_int=True)
+    assert torch.equal(got_int.to(torch.int64), exp_int)
+    exp = orc.gemm_epilogue(exp_int, bias, dtype, 16)
+    assert torch.equal(got.view(torch.uint8), exp.view(torch.uint8))
+
+
+def test_portable_strided_operands():
+    a = _rand((40, 96), torch.float32, 4)
+    w = _rand((24, 96), torch.float32, 5)  # (N, K) weight viewed as (K, N)
+    with L.overrides(gemm_portable=True):
+        got = _gemm(a.cuda()[::2], w.cuda().t(), None, 64, 16).cpu()
+    exp = orc.gemm_fxp(a[::2], w.t(), None, 64, 16, sequential=True)
+    assert torch.equal(got, exp)
+
+
+# ---------------- default route: tolerance + invariance (all dtypes) ----------------
+
+@pytest.mark.parametrize("dtype", _DTYPES)
+@pytest.mark.parametrize("M,N,K", [(8, 16, 32), (4, 4, 64), (130, 130, 33), (256, 256, 256),
+                                   (100, 384, 512), (300, 264, 1096)])
+@pytest.mark.parametrize("use_bias", [False, True])
+def test_matches_float_matmul(dtype, M, N, K, use_bias):
+    a = _rand((M, K), dtype, 11, 0.5).cuda()
+    b = _rand((K, N), dtype, 12, 0.5).cuda()
+    bias = _rand((N,), dtype, 13).cuda() if use_bias else None
+    got = _gemm(a, b, bias)
+    assert got.dtype == dtype and got.shape == (M, N)
+    ref = a.float() @ b.float()
+    if use_bias:
+        ref = ref + bias.float()
+    atol, rtol = _TOL[dtype]
+    assert torch.allclose(got.float(), ref.to(dtype).float(), atol=atol * max(1.0, K / 64) ** 0.5,
+                          rtol=rtol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("M,N,K,kt", [(128, 256, 512, 64), (200, 320, 1024, 128), (64, 4096, 1024, 64)])
+def test_int_accumulators_close_to_oracle(dtype, M, N, K, kt):
+    a = _rand((M, K), dtype, 21).cuda()
+    b = _rand((K, N), dtype, 22, 0.05).cuda()
+    with L.overrides(gemm_k_tile=kt, gemm_split_k=1):
+        got = torch.ops.fxpr.gemm_fxp_int(a, b, 64, 16).cpu()
+    exp = orc.gemm_fxp(a.cpu(), b.cpu(), None, 64, 16, k_tile=kt, return_int=True)
+    # each K-tile's partial can differ in its last fp32 ulp -> at most one LSB per tile
+    assert (got - exp).abs().max().item() <= K // kt
+    assert (got - exp).abs().float().mean().item() < 0.25
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("int_bits", [32, 64])
+def test_integer_stage_exact_given_kernel_partials(dtype, int_bits):
+    M, N, K, kt = 150, 264, 640, 64
+    a = _rand((M, K), dtype, 31, 2.0).cuda()
+    b = _rand((K, N), dtype, 32, 2.0).cuda()
+    a[0, :] = 3000.0  # rows that saturate a Q16.16/int32 tile and wrap the sum
+    b[:, 0] = 3000.0
+    with L.overrides(gemm_k_tile=kt, gemm_split_k=1, gemm_partials=True) as o:
+        got = torch.ops.fxpr.gemm_fxp_int(a, b, int_bits, 16).cpu()
+        partials = o.last_partials.cpu()
+    exp = orc.gemm_int_from_partials(partials, int_bits, 16)
+    assert torch.equal(got.to(torch.int64), exp)
+
+
+@pytest.mark.parametrize("dtype", _DTYPES)
+def test_deterministic_across_runs(dtype):
+    a = _rand((200, 512), dtype, 41).cuda()
+    b = _rand((512, 136), dtype, 42).cuda()
+    first = _gemm(a, b)
+    for _ in range(4):
+        assert torch.equal(first, _gemm(a, b))
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("M,N,K", [(64, 512, 2048), (300, 264, 1096), (1, 128, 4096)])
+@pytest.mark.parametrize("kt", [64, 128])
+def test_split_k_invariance(dtype, M, N, K, kt):
+    a = _rand((M, K), dtype, 51).cuda()
+    b = _rand((K, N), dtype, 52, 0.05).cuda()
+    bias = _rand((N,), dtype, 53).cuda()
+    outs = []
+    for split in (1, 2, 4, 8, 16):
+        with L.overrides(gemm_k_tile=kt, gemm_split_k=split):
+            outs.append((_gemm(a, b, bias, 64, 16), torch.ops.fxpr.gemm_fxp_int(a, b, 64, 16)))
+    for c, ci in outs[1:]:
+        assert torch.equal(c, outs[0][0]) and torch.equal(ci, outs[0][1])
+    # scratch is left clean: a second sweep gives the same bits
+    with L.overrides(gemm_k_tile=kt, gemm_split_k=4):
+        assert torch.equal(_gemm(a, b, bias, 64, 16), outs[0][0])
+
+
+@pytest.mark.parametrize("dtype", _DTYPES)
+def test_ktile_permutation_invariance(dtype):
+    kt = L.BLOCK_K_BY_DTYPE[dtype]
+    M, K, N = 4, kt * 4, 8
+    a = _rand((M, K), dtype, 61).cuda()
+    b = _rand((K, N), dtype, 62).cuda()
+    tperm = torch.randperm(4)
+    perm = torch.cat([torch.arange(t * kt, (t + 1) * kt) for t in tperm]).cuda()
+    assert torch.equal(_gemm(a, b), _gemm(a[:, perm].contiguous(), b[perm].contiguous()))
+
+
+@pytest.mark.parametrize("dtype", _DTYPES)
+@pytest.mark.parametrize("K,N", [(64, 16), (512, 264)])
+def test_batch_size_invariance(dtype, K, N):
+    a_full = _rand((300, K), dtype, 71).cuda()
+    b = _rand((K, N), dtype, 72).cuda()
+    rows = [0, 3, 17, 64, 127, 299]
+    refs = {m: _gemm(a_full[m:m + 1], b)[0] for m in rows}
+    for batch in (1, 4, 16, 128, 300):
+        out = _gemm(a_full[:batch], b)
+        for m in rows:
+            if m < batch:
+                assert torch.equal(out[m], refs[m]), f"row {m} differs at batch={batch}"
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_tensor_core_route_agrees_with_cuda_core_route(dtype):
+    a = _rand((96, 512), dtype, 81).cuda()
+    b = _rand((512, 128), dtype, 82, 0.1).cuda()
+    tc = torch.ops.fxpr.gemm_fxp_int(a, b, 64, 16)
+    with L.overrides(gemm_portable=True):
+        cc = torch.ops.fxpr.gemm_fxp_int(a, b, 64, 16)
+    assert (tc - cc).abs().max().item() <= 512 // L.BLOCK_K_BY_DTYPE[dtype]
+
+
+def test_identity_zero_and_empty():
+    a = _rand((4, 16), torch.float32, 91).cuda()
+    assert torch.allclose(_gemm(a, torch.eye(16, device="cuda")), a, atol=1e-4)
+    z = _gemm(torch.ones((4, 16), device="cuda"), torch.zeros((16, 4), device="cuda"))
+    assert torch.equal(z, torch.zeros((4, 4), device="cuda"))
+    e = _gemm(torch.empty((0, 16), device="cuda"), torch.zeros((16, 4), device="cuda"))
+    assert e.shape == (0, 4)
+    with pytest.raises(ValueError):
+        _gemm(a, torch.eye(16, device="cuda"), None, 24, 16)
+
+
+def test_epilogue_from_int_matches_oracle():
+    g = torch.Generator().manual_seed(5)
+    ci = torch.randint(-(2**40), 2**40, (37, 53), generator=g, dtype=torch.int64)
+    bias = torch.randn(53, generator=g).to(torch.bfloat16)
+    got = torch.ops.fxpr.gemm_fxp_epilogue(ci.cuda(), bias.cuda(), torch.bfloat16, 16).cpu()
+    exp = orc.gemm_epilogue(ci, bias, torch.bfloat16, 16)
+    assert torch.equal(got.view(torch.uint8), exp.view(torch.uint8))
+
+
+def test_tp_sharding_single_gpu_equals_unsharded():
+    # row-parallel layer: K sharded over "ranks", integer accumulators summed
+    a = _rand((64, 4096), torch.bfloat16, 95).cuda()
+    b = _rand((4096, 512), torch.bfloat16, 96, 0.02).cuda()
+    full = torch.ops.fxpr.gemm_fxp_int(a, b, 64, 16)
+    for tp in (2, 4, 8):
+        ks = 4096 // tp
+        acc = torch.zeros_like(full)
+        for r in range(tp):
+            acc += torch.ops.fxpr.gemm_fxp_int(a[:, r * ks:(r + 1) * ks], b[r * ks:(r + 1) * ks], 64, 16)
+        assert torch.equal(acc, full)
+    out = torch.ops.fxpr.gemm_fxp_epilogue(full, None, torch.bfloat16, 16)
+    assert torch.equal(out, _gemm(a, b, None, 64, 16))

@@ -1,0 +1,198 @@
+// Row-wise log-softmax with an integer (int64 Q-format) sum of exponentials.
+//
+//   m = max_i x_i (exact)          e_i = exp2_det((x_i - m) * log2 e)
+//   S = sum_i Q(e_i)  (int64)      y_i = (x_i - m) - log_det(fp32(S) * 2^-frac)
+//
+// The reference has no such kernel (its README lists sampler files that are
+// absent); this is the order-free replacement for the float log_softmax of
+// vLLM's Sampler.compute_logprobs.
+//
+// A row is split over a thread-block cluster of 1..8 CTAs; each CTA keeps its
+// slice in shared memory as fp32, so HBM is read once and written once.  The
+// row maximum and the integer sum are exchanged through distributed shared
+// memory (every CTA reads every peer's slot; max and integer add are order-free).
+// Rows too long for 8 x shared memory fall back to re-reading the slice.
+#include <cooperative_groups.h>
+
+#include "fxp_common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace fxpr {
+
+static constexpr int kLsmThreads = 256;
+static constexpr int kLsmMaxSliceBytes = 200 * 1024;
+
+template <typename T, int VEC>
+struct alignas(sizeof(T) * VEC) LsPack {
+  T v[VEC];
+};
+
+// slice: elements [begin, end) of the row handled by this CTA; `begin` is a
+// multiple of VEC so vector accesses stay aligned.
+template <typename T, int VEC, bool CACHE>
+__global__ void __launch_bounds__(kLsmThreads)
+log_softmax_kernel(const T* __restrict__ x, float* __restrict__ y, int cols, int slice_len,
+                   float scale, float inv_scale, bool wide_q) {
+  extern __shared__ __align__(16) float slice[];
+  __shared__ long long red_i[32];
+  __shared__ float red_f[32];
+  __shared__ float xchg_max;        // read by peer CTAs
+  __shared__ long long xchg_sum;    // read by peer CTAs
+  __shared__ float bc_log;
+
+  cg::cluster_group cluster = cg::this_cluster();
+  const unsigned csize = cluster.num_blocks();
+  const unsigned crank = cluster.block_rank();
+  const int64_t row = blockIdx.x / csize;
+  const int begin = (int)crank * slice_len;
+  const int end = min(cols, begin + slice_len);
+  const int len = max(0, end - begin);
+  const T* xr = x + row * (int64_t)cols + begin;
+  float* yr = y + row * (int64_t)cols + begin;
+  const int nvec = len / VEC;
+  const float ninf = -__int_as_float(0x7f800000);
+
+  // ---- phase 1: load the slice, local maximum --------------------------------
+  float lmax = ninf;
+  for (int c = threadIdx.x; c < nvec; c += blockDim.x) {
+    LsPack<T, VEC> p = *reinterpret_cast<const LsPack<T, VEC>*>(xr + c * VEC);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+      const float v = to_f32<T>(p.v[j]);
+      if (CACHE) slice[c * VEC + j] = v;
+      lmax = fmaxf(lmax, v);
+    }
+  }
+  for (int i = nvec * VEC + threadIdx.x; i < len; i += blockDim.x) {
+    const float v = to_f32<T>(xr[i]);
+    if (CACHE) slice[i] = v;
+    lmax = fmaxf(lmax, v);
+  }
+  lmax = block_max_f32(lmax, red_f);
+  if (threadIdx.x == 0) xchg_max = lmax;
+  cluster.sync();
+  float gmax = ninf;
+  for (unsigned r = 0; r < csize; ++r) gmax = fmaxf(gmax, *cluster.map_shared_rank(&xchg_max, r));
+
+  // ---- phase 2: integer sum of exponentials ------------------------------------
+  unsigned long long acc = 0;
+  auto add_one = [&](float v) {
+    const float e = exp2_det(__fmul_rn(__fsub_rn(v, gmax), FXPR_LOG2E_F32));
+    // e is in [0, 1]: it fits 32 bits unless frac_bits > 30.
+    if (wide_q) acc += (unsigned long long)float_to_fixed<64>(e, scale);
+    else acc += (unsigned long long)(long long)float_to_fixed<32>(e, scale);
+  };
+  if (CACHE) {
+    for (int i = threadIdx.x; i < len; i += blockDim.x) add_one(slice[i]);
+  } else {
+    for (int i = threadIdx.x; i < len; i += blockDim.x) add_one(to_f32<T>(xr[i]));
+  }
+  const long long lsum = block_sum_i64((long long)acc, red_i);
+  if (threadIdx.x == 0) xchg_sum = lsum;
+  cluster.sync();
+  if (threadIdx.x == 0) {
+    long long total = 0;
+    for (unsigned r = 0; r < csize; ++r) total += *cluster.map_shared_rank(&xchg_sum, r);
+    bc_log = log_det(fixed_to_float<long long>(total, inv_scale));
+  }
+  __syncthreads();
+  const float lg = bc_log;
+
+  // ---- phase 3: write the slice ---------------------------------------------------
+  const bool y_vec = (((uintptr_t)yr) & 15) == 0;
+  if (CACHE && y_vec) {
+    const int n4 = len / 4;
+    for (int c = threadIdx.x; c < n4; c += blockDim.x) {
+      float4 v = *reinterpret_cast<const float4*>(slice + c * 4);
+      v.x = __fsub_rn(__fsub_rn(v.x, gmax), lg);
+      v.y = __fsub_rn(__fsub_rn(v.y, gmax), lg);
+      v.z = __fsub_rn(__fsub_rn(v.z, gmax), lg);
+      v.w = __fsub_rn(__fsub_rn(v.w, gmax), lg);
+      *reinterpret_cast<float4*>(yr + c * 4) = v;
+    }
+    for (int i = n4 * 4 + threadIdx.x; i < len; i += blockDim.x)
+      yr[i] = __fsub_rn(__fsub_rn(slice[i], gmax), lg);
+  } else {
+    for (int i = threadIdx.x; i < len; i += blockDim.x) {
+      const float v = CACHE ? slice[i] : to_f32<T>(xr[i]);
+      yr[i] = __fsub_rn(__fsub_rn(v, gmax), lg);
+    }
+  }
+  // Peers may still be reading this CTA's exchange slots.
+  cluster.sync();
+}
+
+template <typename T>
+static int launch_lsm(const void* x, float* y, int64_t rows, int cols, float scale, float inv,
+                      bool wide_q, cudaStream_t s) {
+  constexpr int V = 16 / sizeof(T);
+  // Smallest cluster whose slice fits comfortably (<= 64 KB keeps 3 CTAs per SM),
+  // else the smallest that fits at all, else 8 with re-reads.
+  int csize = 1;
+  auto slice_of = [&](int c) {
+    int sl = (cols + c - 1) / c;
+    return ((sl + 15) / 16) * 16;  // multiple of 16 elements: aligned for every dtype
+  };
+  while (csize < 8 && (size_t)slice_of(csize) * 4 > 64 * 1024) csize *= 2;
+  int slice_len = slice_of(csize);
+  const bool cache = (size_t)slice_len * 4 <= (size_t)kLsmMaxSliceBytes;
+  const bool vec_ok = (cols % V == 0) && ((((uintptr_t)x) & 15) == 0);
+  const size_t smem = cache ? (size_t)slice_len * 4 : 0;
+
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(rows * csize));
+  cfg.blockDim = dim3(kLsmThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = csize;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+
+  const T* xp = (const T*)x;
+  cudaError_t e;
+#define FXPR_LSM_LAUNCH(VV, CC)                                                              \
+  do {                                                                                       \
+    auto k = log_softmax_kernel<T, VV, CC>;                                                  \
+    if (smem > 48 * 1024) {                                                                  \
+      e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize,               \
+                               kLsmMaxSliceBytes);                                           \
+      if (e != cudaSuccess) { set_last_error("log_softmax smem attribute", e); return FXPR_ERR_CUDA; } \
+    }                                                                                        \
+    e = cudaLaunchKernelEx(&cfg, k, xp, y, cols, slice_len, scale, inv, wide_q);             \
+  } while (0)
+  if (cache) {
+    if (vec_ok) FXPR_LSM_LAUNCH(V, true); else FXPR_LSM_LAUNCH(1, true);
+  } else {
+    if (vec_ok) FXPR_LSM_LAUNCH(V, false); else FXPR_LSM_LAUNCH(1, false);
+  }
+#undef FXPR_LSM_LAUNCH
+  if (e != cudaSuccess) { set_last_error("log_softmax launch", e); return FXPR_ERR_CUDA; }
+  return check_launch("log_softmax");
+}
+
+}  // namespace fxpr
+
+using namespace fxpr;
+
+extern "C" int fxpr_log_softmax(const void* x, int x_dtype, float* y, int64_t rows, int64_t cols,
+                                int frac_bits, void* stream) {
+  if (rows < 0 || cols < 0 || frac_bits < 0 || frac_bits > 32) return FXPR_ERR_BAD_ARG;
+  if (rows == 0 || cols == 0) return FXPR_OK;
+  if (!x || !y) return FXPR_ERR_BAD_ARG;
+  if (cols > (int64_t)1 << 30 || rows * 8 > 0x7fffffffLL) return FXPR_ERR_BAD_ARG;
+  const float scale = (float)(1ull << frac_bits);
+  const float inv = 1.0f / scale;
+  const bool wide_q = frac_bits > 30;
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (x_dtype) {
+    case FXPR_F32: return launch_lsm<float>(x, y, rows, (int)cols, scale, inv, wide_q, s);
+    case FXPR_F16: return launch_lsm<__half>(x, y, rows, (int)cols, scale, inv, wide_q, s);
+    case FXPR_BF16: return launch_lsm<__nv_bfloat16>(x, y, rows, (int)cols, scale, inv, wide_q, s);
+  }
+  return FXPR_ERR_UNSUPPORTED;
+}

@@ -1,0 +1,537 @@
+"""``torch.ops.fxpr.*`` schemas and their CUDA implementations.
+
+The six schema strings are those of ``fxpr_vllm/_lib.py:15-33`` in the
+reference, so vLLM-side code written against the reference keeps working.
+Implementations are registered for the CUDA dispatch key only (CPU tensors get
+the dispatcher's ``NotImplementedError``, as with the reference) and hand raw
+pointers plus the current stream to the C ABI in ``libfxpr_b200.so``.
+
+Three ops are additions with no counterpart in the reference:
+``log_softmax_fxp`` (order-free sampler log-softmax), ``gemm_fxp_int`` and
+``gemm_fxp_epilogue`` (integer accumulators out / back in, for the
+tensor-parallel integer all-reduce).
+"""
+from __future__ import annotations
+
+import contextlib
+import math
+import threading
+
+import torch
+
+from . import _native as nat
+from .config import get_runtime_config
+
+_lib = torch.library.Library("fxpr", "DEF")
+
+_lib.define("float_to_fixed(Tensor x, int int_bits, int fxp_frac_bits) -> Tensor")
+_lib.define("fixed_to_float(Tensor x, int float_bits, int fxp_frac_bits) -> Tensor")
+_lib.define("rms_norm_fxp(Tensor x, Tensor weight_fp32, float eps) -> Tensor")
+_lib.define(
+    "rms_norm_fxp_residual(Tensor x, Tensor(a!) residual, Tensor weight_fp32, "
+    "float eps) -> Tensor"
+)
+_lib.define(
+    "gemm_fxp(Tensor a, Tensor b, Tensor? bias, int fxp_int_bits, "
+    "int fxp_frac_bits) -> Tensor"
+)
+_lib.define(
+    "unified_attention_fxp(Tensor q, Tensor kv_cache, Tensor(a!) o, "
+    "Tensor query_start_loc, Tensor seq_lens, Tensor block_table, "
+    "int max_query_len, Tensor? alibi_slopes, bool is_causal, "
+    "float? softmax_scale, int fxp_int_bits, int fxp_frac_bits, "
+    "float logit_softcap, int window_size, int num_kv_splits) -> ()"
+)
+# additions
+_lib.define("log_softmax_fxp(Tensor x, int fxp_frac_bits) -> Tensor")
+_lib.define("gemm_fxp_int(Tensor a, Tensor b, int fxp_int_bits, int fxp_frac_bits) -> Tensor")
+_lib.define(
+    "gemm_fxp_epilogue(Tensor c_int, Tensor? bias, ScalarType out_dtype, "
+    "int fxp_frac_bits) -> Tensor"
+)
+
+_INT_DTYPE = {16: torch.int16, 32: torch.int32, 64: torch.int64}
+_INT_BITS = {v: k for k, v in _INT_DTYPE.items()}
+_FLOAT_DTYPE = {16: torch.float16, 32: torch.float32, 64: torch.float64}
+
+_CAST_FLOAT_DTYPES = (torch.float16, torch.float32, torch.float64)  # casts.py:14
+_IO_DTYPES = (torch.float32, torch.float16, torch.bfloat16)
+
+# K-tile = determinism granularity per dtype (gemm.py:26-30 of the reference);
+# tests read this the way the reference's test reads _BLOCK_K_BY_DTYPE.
+BLOCK_K_BY_DTYPE = {torch.float16: 128, torch.bfloat16: 128, torch.float32: 64}
+# key-tile width of the attention kernels (attention.py:32-36)
+BLOCK_N_BY_DTYPE = {torch.float16: 64, torch.bfloat16: 64, torch.float32: 32}
+
+
+def _check_frac_bits(n: int) -> None:
+    if int(n) not in (8, 16, 32):
+        raise ValueError(f"fxp_frac_bits must be 8/16/32, got {n}")
+
+
+def _check_int_bits(n: int) -> None:
+    if int(n) not in (16, 32, 64):
+        raise ValueError(f"int_bits must be 16/32/64, got {n}")
+
+
+@contextlib.contextmanager
+def _on_device(t: torch.Tensor):
+    """Make ``t``'s device current for the duration of a C call."""
+    if t.device.index is not None and t.device.index != torch.cuda.current_device():
+        with torch.cuda.device(t.device):
+            yield
+    else:
+        yield
+
+
+# --------------------------------------------------------------------------
+# test / tuning overrides (the public schemas carry no such arguments)
+# --------------------------------------------------------------------------
+
+class _Overrides(threading.local):
+    gemm_k_tile: int | None = None
+    gemm_split_k: int | None = None
+    gemm_portable: bool = False
+    attn_portable: bool = False
+    gemm_partials: bool = False
+    last_partials: torch.Tensor | None = None
+
+
+_ovr = _Overrides()
+
+
+@contextlib.contextmanager
+def overrides(*, gemm_k_tile=None, gemm_split_k=None, gemm_portable=None,
+              attn_portable=None, gemm_partials=None):
+    """Temporarily pin kernel-selection knobs (K-tile, split-K, portable route)."""
+    names = ("gemm_k_tile", "gemm_split_k", "gemm_portable", "attn_portable", "gemm_partials")
+    vals = (gemm_k_tile, gemm_split_k, gemm_portable, attn_portable, gemm_partials)
+    old = {n: getattr(_ovr, n) for n in names}
+    try:
+        for n, v in zip(names, vals):
+            if v is not None:
+                setattr(_ovr, n, v)
+        yield _ovr
+    finally:
+        for n, v in old.items():
+            setattr(_ovr, n, v)
+
+
+# --------------------------------------------------------------------------
+# casts
+# --------------------------------------------------------------------------
+
+def float_to_fixed_run(x: torch.Tensor, int_bits: int, fxp_frac_bits: int) -> torch.Tensor:
+    """casts.py:57-89 of the reference."""
+    if not x.is_cuda:
+        raise RuntimeError("float_to_fixed: input must be CUDA")
+    if x.dtype not in _CAST_FLOAT_DTYPES:
+        raise TypeError(
+            f"float_to_fixed: unsupported input dtype {x.dtype}; "
+            f"expected one of {_CAST_FLOAT_DTYPES}"
+        )
+    if int_bits not in _INT_DTYPE:
+        raise ValueError(f"int_bits must be 16/32/64, got {int_bits}")
+    if not (0 <= fxp_frac_bits < 64):
+        raise ValueError(f"frac_bits must satisfy 0 <= N < 64, got {fxp_frac_bits}")
+    x_c = x.contiguous()
+    y = torch.empty_like(x_c, dtype=_INT_DTYPE[int_bits])
+    n = x_c.numel()
+    if n == 0:
+        return y
+    with _on_device(x_c):
+        st = nat.load().fxpr_float_to_fixed(
+            x_c.data_ptr(), nat.DTYPE_CODE[x_c.dtype], y.data_ptr(), int_bits,
+            fxp_frac_bits, n, nat.stream_ptr(x_c.device))
+    nat.check(st, "float_to_fixed")
+    return y
+
+
+def fixed_to_float_run(x: torch.Tensor, float_bits: int, fxp_frac_bits: int) -> torch.Tensor:
+    """casts.py:92-126 of the reference."""
+    if not x.is_cuda:
+        raise RuntimeError("fixed_to_float: input must be CUDA")
+    if x.dtype not in _INT_BITS:
+        raise TypeError(
+            f"fixed_to_float: unsupported input dtype {x.dtype}; "
+            f"expected one of {tuple(_INT_BITS)}"
+        )
+    if float_bits not in _FLOAT_DTYPE:
+        raise ValueError(f"float_bits must be 16/32/64, got {float_bits}")
+    if not (0 <= fxp_frac_bits < 64):
+        raise ValueError(f"fxp_frac_bits must satisfy 0 <= N < 64, got {fxp_frac_bits}")
+    x_c = x.contiguous()
+    y = torch.empty_like(x_c, dtype=_FLOAT_DTYPE[float_bits])
+    n = x_c.numel()
+    if n == 0:
+        return y
+    with _on_device(x_c):
+        st = nat.load().fxpr_fixed_to_float(
+            x_c.data_ptr(), _INT_BITS[x_c.dtype], y.data_ptr(), float_bits,
+            fxp_frac_bits, n, nat.stream_ptr(x_c.device))
+    nat.check(st, "fixed_to_float")
+    return y
+
+
+# --------------------------------------------------------------------------
+# RMSNorm
+# --------------------------------------------------------------------------
+
+def _rms_norm_launch(x, w, residual, eps):
+    """rms_norm.py:78-134 of the reference (same checks, same contiguity rules)."""
+    if not x.is_cuda or not w.is_cuda:
+        raise RuntimeError("rms_norm: x and w must be CUDA")
+    if x.dtype not in _IO_DTYPES:
+        raise TypeError(
+            f"rms_norm: unsupported input dtype {x.dtype}; expected one of {_IO_DTYPES}"
+        )
+    if w.dtype != x.dtype:
+        raise TypeError("rms_norm: weight dtype must match input dtype")
+    if residual is not None:
+        if not residual.is_cuda:
+            raise RuntimeError("rms_norm: residual must be CUDA")
+        if residual.dtype != x.dtype:
+            raise TypeError("rms_norm: residual dtype must match input dtype")
+        if residual.shape != x.shape:
+            raise ValueError("rms_norm: residual shape must match x")
+
+    hidden = x.shape[-1]
+    x_2d = x.reshape(-1, hidden).contiguous()
+    y_2d = torch.empty_like(x_2d)
+    r_storage = None
+    if residual is not None:
+        r_2d = residual.reshape(-1, hidden)
+        r_storage = r_2d if r_2d.is_contiguous() else r_2d.contiguous()
+    rows = x_2d.shape[0]
+    if rows > 0 and hidden > 0:
+        w_c = w.contiguous()
+        with _on_device(x_2d):
+            st = nat.load().fxpr_rms_norm(
+                x_2d.data_ptr(), nat.ptr(r_storage), w_c.data_ptr(), y_2d.data_ptr(),
+                nat.DTYPE_CODE[x.dtype], rows, hidden, float(eps),
+                get_runtime_config().fxp_frac_bits, nat.stream_ptr(x.device))
+        nat.check(st, "rms_norm")
+    if residual is not None and r_storage.data_ptr() != residual.data_ptr():
+        residual.copy_(r_storage.view_as(residual))
+    return y_2d.view_as(x)
+
+
+def rms_norm_fxp_run(x, w, eps):
+    return _rms_norm_launch(x, w, None, eps)
+
+
+def rms_norm_fxp_residual_run(x, residual, w, eps):
+    return _rms_norm_launch(x, w, residual, eps)
+
+
+# --------------------------------------------------------------------------
+# log-softmax
+# --------------------------------------------------------------------------
+
+def log_softmax_fxp_run(x: torch.Tensor, fxp_frac_bits: int) -> torch.Tensor:
+    if not x.is_cuda:
+        raise RuntimeError("log_softmax_fxp: input must be CUDA")
+    if x.dtype not in _IO_DTYPES:
+        raise TypeError(f"log_softmax_fxp: unsupported input dtype {x.dtype}")
+    cols = x.shape[-1] if x.dim() > 0 else 1
+    x_2d = x.reshape(-1, cols).contiguous()
+    y = torch.empty(x_2d.shape, device=x.device, dtype=torch.float32)
+    if x_2d.numel() > 0:
+        with _on_device(x_2d):
+            st = nat.load().fxpr_log_softmax(
+                x_2d.data_ptr(), nat.DTYPE_CODE[x.dtype], y.data_ptr(), x_2d.shape[0], cols,
+                fxp_frac_bits, nat.stream_ptr(x.device))
+        nat.check(st, "log_softmax_fxp")
+    return y.view(x.shape)
+
+
+# --------------------------------------------------------------------------
+# GEMM
+# --------------------------------------------------------------------------
+
+_gemm_scratch: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def _get_gemm_scratch(device: torch.device, nbytes: int) -> torch.Tensor:
+    """Persistent zero-initialised split-K scratch per device, grown on demand
+    (the kernel re-zeroes what it used; gemm.py:86-107 of the reference keeps
+    one such buffer too).  Grow it before CUDA-graph capture (``warmup_gemm``)."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    cur = _gemm_scratch.get((idx, 0))
+    if cur is None or cur.numel() < nbytes:
+        cur = torch.zeros(max(nbytes, 1 << 20), device=device, dtype=torch.uint8)
+        _gemm_scratch[(idx, 0)] = cur
+    return cur
+
+
+_SM_COUNT: dict[int, int] = {}
+
+
+def _sm_count(device: torch.device) -> int:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    n = _SM_COUNT.get(idx)
+    if n is None:
+        n = torch.cuda.get_device_properties(idx).multi_processor_count
+        _SM_COUNT[idx] = n
+    return n
+
+
+def pick_split_k(M: int, N: int, K: int, k_tile: int, int_bits: int, num_sms: int) -> int:
+    """Host-shape-only split-K policy (both routes give the same bits, so this
+    is a speed decision only; the reference times it at warmup instead,
+    gemm.py:780-836).  Split when the output tiles alone cannot fill the GPU."""
+    if int_bits == 16:
+        return 1
+    tiles_mn = -(-M // 128) * -(-N // 128)
+    k_tiles = -(-K // k_tile)
+    if tiles_mn >= num_sms or k_tiles < 8:
+        return 1
+    split = 1
+    while split < 16 and tiles_mn * split * 2 <= num_sms * 2 and k_tiles // (split * 2) >= 4:
+        split *= 2
+    return split
+
+
+def _gemm_common(a, b, bias, int_bits, frac_bits, want_c: bool, want_int: bool):
+    M, K = a.shape
+    N = b.shape[1]
+    c = torch.empty((M, N), device=a.device, dtype=a.dtype) if want_c else None
+    c_int = torch.empty((M, N), device=a.device, dtype=_INT_DTYPE[int_bits]) if want_int else None
+    if M == 0 or N == 0:
+        return c, c_int
+    if a.dtype not in _IO_DTYPES or b.dtype != a.dtype:
+        raise TypeError(f"gemm_fxp: unsupported dtypes {a.dtype} x {b.dtype}")
+    cfg = get_runtime_config()
+    k_tile = _ovr.gemm_k_tile if _ovr.gemm_k_tile is not None else cfg.gemm_k_tile
+    if not k_tile:
+        k_tile = BLOCK_K_BY_DTYPE[a.dtype]
+    split_k = _ovr.gemm_split_k if _ovr.gemm_split_k is not None else cfg.gemm_split_k
+    if not split_k:
+        split_k = pick_split_k(M, N, K, k_tile, int_bits, _sm_count(a.device))
+    split_k = max(1, min(split_k, -(-K // k_tile) if K else 1))
+    flags = nat.GEMM_FORCE_PORTABLE if _ovr.gemm_portable else 0
+    lib = nat.load()
+    scratch = None
+    scratch_bytes = 0
+    partials = None
+    if _ovr.gemm_partials and split_k == 1:
+        partials = torch.zeros((-(-K // k_tile) if K else 0, M, N), device=a.device,
+                               dtype=torch.float32)
+        _ovr.last_partials = partials
+    if split_k > 1:
+        scratch_bytes = lib.fxpr_gemm_scratch_bytes(M, N, int_bits, split_k)
+        scratch = _get_gemm_scratch(a.device, scratch_bytes)
+    if bias is not None and bias.dtype != a.dtype:
+        bias = bias.to(a.dtype)
+    with _on_device(a):
+        st = lib.fxpr_gemm(
+            a.data_ptr(), b.data_ptr(), nat.ptr(bias), nat.ptr(c), nat.ptr(c_int),
+            nat.DTYPE_CODE[a.dtype], M, N, K, a.stride(0), a.stride(1), b.stride(0), b.stride(1),
+            c.stride(0) if c is not None else N, int_bits, frac_bits, k_tile, split_k, flags,
+            nat.ptr(scratch), scratch_bytes, nat.ptr(partials if partials is not None and partials.numel() else None),
+            nat.stream_ptr(a.device))
+    nat.check(st, "gemm_fxp")
+    return c, c_int
+
+
+def gemm_fxp_run(a, b, bias, int_bits, fxp_frac_bits):
+    """gemm.py:612-763 of the reference (no autotune: the kernels are AOT)."""
+    c, _ = _gemm_common(a, b, bias, int_bits, fxp_frac_bits, True, False)
+    return c
+
+
+def gemm_fxp_int_run(a, b, int_bits, fxp_frac_bits):
+    _, c_int = _gemm_common(a, b, None, int_bits, fxp_frac_bits, False, True)
+    return c_int
+
+
+def gemm_fxp_epilogue_run(c_int, bias, out_dtype, fxp_frac_bits):
+    if c_int.dtype not in _INT_BITS:
+        raise TypeError(f"gemm_fxp_epilogue: c_int must be an integer tensor, got {c_int.dtype}")
+    if out_dtype not in _IO_DTYPES:
+        raise TypeError(f"gemm_fxp_epilogue: unsupported output dtype {out_dtype}")
+    c_int = c_int.contiguous()
+    M, N = c_int.shape
+    c = torch.empty((M, N), device=c_int.device, dtype=out_dtype)
+    if M == 0 or N == 0:
+        return c
+    if bias is not None and bias.dtype != out_dtype:
+        bias = bias.to(out_dtype)
+    with _on_device(c_int):
+        st = nat.load().fxpr_gemm_epilogue_from_int(
+            c_int.data_ptr(), _INT_BITS[c_int.dtype], nat.ptr(bias), c.data_ptr(),
+            nat.DTYPE_CODE[out_dtype], M, N, c.stride(0), fxp_frac_bits,
+            nat.stream_ptr(c_int.device))
+    nat.check(st, "gemm_fxp_epilogue")
+    return c
+
+
+# --------------------------------------------------------------------------
+# attention
+# --------------------------------------------------------------------------
+
+_MIN_KV_TILES_FOR_SPLIT = 32   # attention.py:46-48 of the reference
+_MAX_NUM_SPLITS = 8
+_SPLIT_BASE_OVERSUB = 2
+
+
+def _next_pow2(n: int) -> int:
+    return 1 if n <= 1 else 1 << (n - 1).bit_length()
+
+
+def pick_num_splits(requested, num_requests, num_q_blocks, num_heads, num_kv_tiles, num_sms):
+    """attention.py:664-689 of the reference: an explicit request wins; otherwise
+    split only long contexts on an under-filled GPU, power of two, at most 8."""
+    if requested >= 1:
+        return requested
+    if num_kv_tiles <= _MIN_KV_TILES_FOR_SPLIT:
+        return 1
+    base = max(1, num_requests * num_q_blocks * num_heads)
+    if base > _SPLIT_BASE_OVERSUB * num_sms:
+        return 1
+    split = min(num_kv_tiles // _MIN_KV_TILES_FOR_SPLIT, _MAX_NUM_SPLITS)
+    return _next_pow2(split) if split >= 2 else 1
+
+
+def unified_attention_fxp_run(q, kv_cache, o, query_start_loc, seq_lens, block_table,
+                              max_query_len, alibi_slopes, is_causal, softmax_scale,
+                              fxp_int_bits, fxp_frac_bits, logit_softcap, window_size,
+                              num_kv_splits):
+    """attention.py:692-953 of the reference: same validation, same split policy."""
+    if not (q.is_cuda and kv_cache.is_cuda and o.is_cuda):
+        raise RuntimeError("unified_attention_fxp: tensors must be CUDA")
+    if q.dtype not in _IO_DTYPES:
+        raise TypeError(f"unified_attention_fxp: unsupported q dtype {q.dtype}")
+    if kv_cache.dim() != 5 or kv_cache.shape[1] != 2:
+        raise ValueError("kv_cache must be (num_blocks, 2, page_size, num_kv_heads, head_dim)")
+    if kv_cache.dtype != q.dtype or o.dtype != q.dtype:
+        raise TypeError("kv_cache and o must share dtype with q")
+    if query_start_loc.dtype != torch.int32:
+        raise TypeError("query_start_loc must be int32")
+    if seq_lens.dtype != torch.int32:
+        raise TypeError("seq_lens must be int32")
+    if block_table.dtype != torch.int32:
+        raise TypeError("block_table must be int32")
+    if num_kv_splits < 0:
+        raise ValueError(f"num_kv_splits must be >= 0, got {num_kv_splits}")
+    has_alibi = alibi_slopes is not None and alibi_slopes.numel() > 0
+    if has_alibi and alibi_slopes.dtype != torch.float32:
+        raise TypeError("alibi_slopes must be float32")
+
+    num_heads, head_dim = q.shape[1], q.shape[2]
+    page_size, num_kv_heads = kv_cache.shape[2], kv_cache.shape[3]
+    num_requests = seq_lens.shape[0]
+    if num_heads % num_kv_heads != 0:
+        raise ValueError("num_heads must be divisible by num_kv_heads")
+    if num_requests == 0 or q.shape[0] == 0:
+        return
+    if q.stride(2) != 1 or o.stride(2) != 1 or kv_cache.stride(4) != 1:
+        raise ValueError("unified_attention_fxp: head_dim must be the unit-stride dimension")
+
+    ss = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(head_dim)
+    block_m = 16 if max_query_len <= 1 else 32
+    block_n = BLOCK_N_BY_DTYPE[q.dtype]
+    num_q_blocks = max(1, -(-max(1, int(max_query_len)) // block_m))
+    max_kv_blocks = block_table.shape[1] if block_table.dim() == 2 else 0
+    num_kv_tiles = -(-max(1, max_kv_blocks * page_size) // block_n)
+    splits = pick_num_splits(int(num_kv_splits), num_requests, num_q_blocks, num_heads,
+                             num_kv_tiles, _sm_count(q.device))
+
+    lib = nat.load()
+    scratch = None
+    scratch_bytes = 0
+    if splits > 1:
+        scratch_bytes = lib.fxpr_attention_scratch_bytes(q.shape[0], num_heads, head_dim,
+                                                         fxp_int_bits, splits)
+        scratch = torch.empty(scratch_bytes, device=q.device, dtype=torch.uint8)
+    alibi = alibi_slopes.contiguous() if has_alibi else None
+    flags = (nat.ATTN_CAUSAL if is_causal else 0) | (nat.ATTN_FORCE_PORTABLE if _ovr.attn_portable else 0)
+    k_cache = kv_cache.select(1, 0)
+    v_cache = kv_cache.select(1, 1)
+    qsl = query_start_loc.contiguous()
+    sl = seq_lens.contiguous()
+    bt_stride = block_table.stride(0) if block_table.dim() == 2 else 0
+    if block_table.dim() == 2 and block_table.stride(1) != 1:
+        block_table = block_table.contiguous()
+        bt_stride = block_table.stride(0)
+    with _on_device(q):
+        st = lib.fxpr_attention(
+            q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), o.data_ptr(),
+            qsl.data_ptr(), sl.data_ptr(), block_table.data_ptr(), nat.ptr(alibi),
+            nat.DTYPE_CODE[q.dtype], q.shape[0], num_requests, num_heads, num_kv_heads,
+            head_dim, page_size, q.stride(0), q.stride(1), o.stride(0), o.stride(1),
+            kv_cache.stride(0), kv_cache.stride(2), kv_cache.stride(3), bt_stride,
+            int(max_query_len), flags, ss, float(logit_softcap), int(window_size),
+            fxp_int_bits, fxp_frac_bits, splits, nat.ptr(scratch), scratch_bytes, None,
+            nat.stream_ptr(q.device))
+    nat.check(st, "unified_attention_fxp")
+
+
+# --------------------------------------------------------------------------
+# dispatcher registrations (CUDA key only)
+# --------------------------------------------------------------------------
+
+@torch.library.impl("fxpr::float_to_fixed", "CUDA", lib=_lib)
+def _float_to_fixed_cuda(x, int_bits, fxp_frac_bits):
+    _check_int_bits(int_bits)
+    _check_frac_bits(fxp_frac_bits)
+    return float_to_fixed_run(x, int(int_bits), int(fxp_frac_bits))
+
+
+@torch.library.impl("fxpr::fixed_to_float", "CUDA", lib=_lib)
+def _fixed_to_float_cuda(x, float_bits, fxp_frac_bits):
+    if int(float_bits) not in (16, 32, 64):
+        raise ValueError(f"float_bits must be 16/32/64, got {float_bits}")
+    _check_frac_bits(fxp_frac_bits)
+    return fixed_to_float_run(x, int(float_bits), int(fxp_frac_bits))
+
+
+@torch.library.impl("fxpr::rms_norm_fxp", "CUDA", lib=_lib)
+def _rms_norm_fxp_cuda(x, weight, eps):
+    return rms_norm_fxp_run(x, weight, float(eps))
+
+
+@torch.library.impl("fxpr::rms_norm_fxp_residual", "CUDA", lib=_lib)
+def _rms_norm_fxp_residual_cuda(x, residual, weight, eps):
+    return rms_norm_fxp_residual_run(x, residual, weight, float(eps))
+
+
+@torch.library.impl("fxpr::gemm_fxp", "CUDA", lib=_lib)
+def _gemm_fxp_cuda(a, b, bias, fxp_int_bits, fxp_frac_bits):
+    _check_int_bits(fxp_int_bits)
+    _check_frac_bits(fxp_frac_bits)
+    return gemm_fxp_run(a, b, bias, int(fxp_int_bits), int(fxp_frac_bits))
+
+
+@torch.library.impl("fxpr::unified_attention_fxp", "CUDA", lib=_lib)
+def _unified_attention_fxp_cuda(q, kv_cache, o, query_start_loc, seq_lens, block_table,
+                                max_query_len, alibi_slopes, is_causal, softmax_scale,
+                                fxp_int_bits, fxp_frac_bits, logit_softcap, window_size,
+                                num_kv_splits):
+    _check_int_bits(fxp_int_bits)
+    _check_frac_bits(fxp_frac_bits)
+    unified_attention_fxp_run(
+        q, kv_cache, o, query_start_loc, seq_lens, block_table, int(max_query_len),
+        alibi_slopes, bool(is_causal),
+        None if softmax_scale is None else float(softmax_scale),
+        int(fxp_int_bits), int(fxp_frac_bits), float(logit_softcap), int(window_size),
+        int(num_kv_splits))
+
+
+@torch.library.impl("fxpr::log_softmax_fxp", "CUDA", lib=_lib)
+def _log_softmax_fxp_cuda(x, fxp_frac_bits):
+    _check_frac_bits(fxp_frac_bits)
+    return log_softmax_fxp_run(x, int(fxp_frac_bits))
+
+
+@torch.library.impl("fxpr::gemm_fxp_int", "CUDA", lib=_lib)
+def _gemm_fxp_int_cuda(a, b, fxp_int_bits, fxp_frac_bits):
+    _check_int_bits(fxp_int_bits)
+    _check_frac_bits(fxp_frac_bits)
+    return gemm_fxp_int_run(a, b, int(fxp_int_bits), int(fxp_frac_bits))
+
+
+@torch.library.impl("fxpr::gemm_fxp_epilogue", "CUDA", lib=_lib)
+def _gemm_fxp_epilogue_cuda(c_int, bias, out_dtype, fxp_frac_bits):
+    _check_frac_bits(fxp_frac_bits)
+    return gemm_fxp_epilogue_run(c_int, bias, out_dtype, int(fxp_frac_bits))
