@@ -107,6 +107,9 @@ int64_t fxpr_gemm_scratch_bytes(int64_t M, int64_t N, int int_bits, int split_k)
  * split_k CTAs per output tile and merged with integer atomics (needs scratch).
  * partials_out: optional fp32 [ceil(K/k_tile), M, N] dump of the per-tile
  * float partials (tests only; must be NULL when split_k > 1).
+ * status_word: optional device int the tensor-core kernel sets to
+ * FXPR_ERR_TIMEOUT if one of its bounded mbarrier waits gave up (the output is
+ * then undefined); the host reads it when it next synchronises.
  * Replaces gemm_fxp_run, fxpr_vllm/_triton/gemm.py:612-763.
  */
 int fxpr_gemm(const void* a, const void* b, const void* bias, void* c, void* c_int,
@@ -114,7 +117,7 @@ int fxpr_gemm(const void* a, const void* b, const void* bias, void* c, void* c_i
               int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, int64_t c_sm,
               int int_bits, int frac_bits, int k_tile, int split_k, int flags,
               void* scratch, int64_t scratch_bytes, float* partials_out,
-              void* stream);
+              int32_t* status_word, void* stream);
 
 /*
  * c = T(fp32(c_int) * 2^-frac + bias): the GEMM epilogue applied to integer

@@ -23,7 +23,7 @@ extern "C" int fxpr_gemm(const void* a, const void* b, const void* bias, void* c
                          int dtype, int64_t M, int64_t N, int64_t K, int64_t a_sm, int64_t a_sk,
                          int64_t b_sk, int64_t b_sn, int64_t c_sm, int int_bits, int frac_bits,
                          int k_tile, int split_k, int flags, void* scratch, int64_t scratch_bytes,
-                         float* partials_out, void* stream) {
+                         float* partials_out, int32_t* status_word, void* stream) {
   if (M < 0 || N < 0 || K < 0) return FXPR_ERR_BAD_ARG;
   if (int_bits != 16 && int_bits != 32 && int_bits != 64) return FXPR_ERR_BAD_ARG;
   if (frac_bits < 0 || frac_bits >= 63) return FXPR_ERR_BAD_ARG;
@@ -41,7 +41,7 @@ extern "C" int fxpr_gemm(const void* a, const void* b, const void* bias, void* c
   g.dtype = dtype; g.M = M; g.N = N; g.K = K;
   g.a_sm = a_sm; g.a_sk = a_sk; g.b_sk = b_sk; g.b_sn = b_sn; g.c_sm = c_sm;
   g.int_bits = int_bits; g.frac_bits = frac_bits; g.k_tile = k_tile; g.split_k = split_k;
-  g.scratch = scratch; g.scratch_bytes = scratch_bytes;
+  g.scratch = scratch; g.scratch_bytes = scratch_bytes; g.status = status_word;
 
   if (!(flags & FXPR_GEMM_FORCE_PORTABLE) && gemm_tc_supported(g)) return gemm_tc(g, s);
   return gemm_portable(a, b, bias, c, c_int, partials_out, dtype, M, N, K, a_sm, a_sk, b_sk, b_sn,

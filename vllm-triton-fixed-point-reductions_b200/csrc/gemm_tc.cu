@@ -1,8 +1,589 @@
-// placeholder, replaced below
+// Fixed-point GEMM on the 5th-generation tensor cores (sm_100a): TMA-fed
+// tcgen05.mma with fp32 accumulators in tensor memory, one FRESH accumulator per
+// K-tile, read back by the epilogue warps (tcgen05.ld), rounded to Q-format and
+// summed as integers in registers.  Semantics: fxpr_vllm/_triton/gemm.py:183-204
+// (persistent kernel) and :273-325 (split-K with integer atomics and a
+// last-arriver epilogue) of the reference.
+//
+// CTA = 10 warps, one CTA per SM, persistent over (output tile, k-split) items:
+//   warp 0      TMA producer: A [128 x 64] and B [64 x BN] bf16/fp16 tiles, 128-byte
+//               swizzle, STAGES-deep mbarrier ring
+//   warp 1      MMA issuer: per K-tile k_tile/16 tcgen05.mma (M=128, N=BN, K=16) into
+//               one of two TMEM accumulator buffers, tcgen05.commit to free smem
+//               stages and to publish the finished K-tile
+//   warps 2..9  epilogue: warp w reads TMEM lanes 32*(w%4).. (a row per thread) and
+//               half of the BN columns; converts and accumulates while the MMA warp
+//               works on the next K-tile in the other TMEM buffer
+// Because every K-tile is quantised before it is added, the integer sum does not
+// depend on tile order, split-K, grid size or which CTA ran what.
+//
+// Every wait is bounded: after ~2 s a waiter raises an abort flag, writes the status
+// word, lets in-flight copies land, frees TMEM and returns.
+#include <cuda.h>
+
+#include <type_traits>
+
 #include "fxp_common.cuh"
 #include "gemm_common.cuh"
+
 namespace fxpr {
-bool gemm_tc_supported(const GemmArgs&) { return false; }
-int gemm_tc(const GemmArgs&, cudaStream_t) { return FXPR_ERR_UNSUPPORTED; }
-int64_t gemm_tc_scratch_bytes(int64_t M, int64_t N, int int_bits) { return M * N * 8 + 4096; }
+
+static constexpr int kBM = 128;           // tile rows = TMEM lanes
+static constexpr int kBK = 64;            // smem stage depth: 64 x 2 B = one 128-byte swizzle row
+static constexpr int kEpiWarps = 8;
+static constexpr int kThreads = (2 + kEpiWarps) * 32;
+static constexpr int kGroupM = 8;
+static constexpr long long kWaitCycles = 4000000000LL;  // ~2 s at 2 GHz
+
+// ---------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
 }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok;
+}
+// Bounded wait.  Returns false when the wait gave up or another thread aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  int spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 63) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitCycles) { *abort_flag = 1; return false; }
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                         uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor (sm_100 format): start address, leading / stride
+// byte offsets (all >> 4), version 1, 128-byte swizzle.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3ffff) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3fff) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3fff) << 32;
+  d |= (uint64_t)1 << 46;   // descriptor version (sm_100)
+  d |= (uint64_t)2 << 61;   // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor for kind::f16: fp32 accumulate, A/B format (0 = f16, 1 = bf16),
+// A K-major, B major-ness selectable, N >> 3 at bit 17, M >> 4 at bit 24.
+__host__ __device__ inline uint32_t make_idesc(int ab_format, int b_mn_major, int n, int m) {
+  uint32_t d = 0;
+  d |= 1u << 4;                         // D format = f32
+  d |= (uint32_t)ab_format << 7;        // A format
+  d |= (uint32_t)ab_format << 10;       // B format
+  d |= (uint32_t)(b_mn_major ? 1 : 0) << 16;
+  d |= (uint32_t)(n >> 3) << 17;
+  d |= (uint32_t)(m >> 4) << 24;
+  return d;
+}
+
+// ---------------------------------------------------------------------------------
+// kernel
+// ---------------------------------------------------------------------------------
+struct TcParams {
+  const void* bias; void* c; void* c_int; float* partials;
+  void* acc_scratch; int32_t* locks; int32_t* status;
+  int M, N, K; int64_t c_sm;
+  int k_tile, split_k, int_bits; float scale, inv_scale;
+  int tiles_m, tiles_n; uint32_t idesc; int b_kmajor; int c_vec_ok;
+};
+
+template <int BN, int STAGES>
+struct SmemLayout {
+  static constexpr int kABytes = kBM * kBK * 2;
+  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarOffset = STAGES * kStageBytes;
+  static constexpr int kTotal = kBarOffset + 256 + 1024;  // barriers + alignment slack
+};
+
+template <typename T, int BN, bool ACC64, int STAGES>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+               const TcParams p) {
+  using L = SmemLayout<BN, STAGES>;
+  using AccT = typename std::conditional<ACC64, long long, int32_t>::type;
+  constexpr int kColsPerThread = BN / 2;      // two epilogue warps share a lane quarter
+  constexpr int kTmemCols = 2 * BN;            // two accumulator buffers (power of two >= 32)
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // SW128 tiles need 1 KB alignment
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t bar_base = smem_base + L::kBarOffset;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
+  auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
+  volatile uint32_t* tmem_slot = (volatile uint32_t*)(smem_gen + L::kBarOffset + 8 * (2 * STAGES + 4));
+  volatile int* abort_flag = (volatile int*)(smem_gen + L::kBarOffset + 8 * (2 * STAGES + 4) + 8);
+  const uint32_t epi_bar = bar_base + 8u * (2 * STAGES + 4) + 16u;   // epilogue-warps-only barrier
+  volatile int* s_last = (volatile int*)(smem_gen + L::kBarOffset + 8 * (2 * STAGES + 4) + 24);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), kEpiWarps); }
+    mbar_init(epi_bar, kEpiWarps);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32((const void*)tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles_mn = p.tiles_m * p.tiles_n;
+  const int items = tiles_mn * p.split_k;
+  const int k_tiles_total = (p.K + p.k_tile - 1) / p.k_tile;
+  const int chunks = p.k_tile / kBK;
+
+  auto tile_coords = [&](int tile, int& pm, int& pn) {
+    const int in_group = kGroupM * p.tiles_n;
+    const int g = tile / in_group;
+    const int first = g * kGroupM;
+    const int gsz = min(p.tiles_m - first, kGroupM);
+    pm = first + (tile % in_group) % gsz;
+    pn = (tile % in_group) / gsz;
+  };
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer --------------------------------
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0; bool ok = true;
+      for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
+        int pm, pn; tile_coords(item / p.split_k, pm, pn);
+        const int ks = item % p.split_k;
+        for (int kt = ks; kt < k_tiles_total && ok; kt += p.split_k) {
+          for (int ch = 0; ch < chunks; ++ch) {
+            if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag)) { ok = false; break; }
+            const uint32_t sa = smem_base + stage * L::kStageBytes;
+            const uint32_t sb = sa + L::kABytes;
+            const int k0 = kt * p.k_tile + ch * kBK;
+            mbar_expect_tx(full_bar(stage), L::kStageBytes);
+            tma_load_2d(sa, &tma_a, full_bar(stage), k0, pm * kBM);
+            if (p.b_kmajor) {
+              // B stored (N, K): rows = n, 64 k contiguous; boxes of 64 rows keep the
+              // tensor-map box <= 256 and the layout identical to A's
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j)
+                tma_load_2d(sb + j * (64 * kBK * 2), &tma_b, full_bar(stage), k0, pn * BN + j * 64);
+            } else {
+              // B stored (K, N): boxes of 64 n (128 B) x 64 k rows
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j)
+                tma_load_2d(sb + j * (64 * kBK * 2), &tma_b, full_bar(stage), pn * BN + j * 64, k0);
+            }
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ----------------------------------
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0; int buf = 0; uint32_t tphase[2] = {0, 0}; bool ok = true;
+      for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
+        const int ks = item % p.split_k;
+        for (int kt = ks; kt < k_tiles_total && ok; kt += p.split_k) {
+          if (!mbar_wait(tempty_bar(buf), tphase[buf] ^ 1, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+          for (int ch = 0; ch < chunks; ++ch) {
+            if (!mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t sa = smem_base + stage * L::kStageBytes;
+            const uint32_t sb = sa + L::kABytes;
+#pragma unroll
+            for (int k = 0; k < kBK / 16; ++k) {
+              // A: K-major, 8-row groups 1024 B apart, +32 B per 16-wide k step
+              const uint64_t adesc = make_smem_desc(sa + k * 32, 16, 1024);
+              // B K-major: same as A.  B N-major: 64-column slabs 8192 B apart (leading
+              // offset), 8-k-row groups 1024 B apart, +2048 B per 16-deep k step
+              const uint64_t bdesc = p.b_kmajor ? make_smem_desc(sb + k * 32, 16, 1024)
+                                                : make_smem_desc(sb + k * 2048, 8192, 1024);
+              umma_f16(d_tmem, adesc, bdesc, p.idesc, (ch | k) ? 1u : 0u);
+            }
+            umma_commit(empty_bar(stage));   // frees the smem stage when these MMAs finish
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          }
+          if (!ok) break;
+          umma_commit(tfull_bar(buf));       // K-tile accumulator complete
+          tphase[buf] ^= 1; buf ^= 1;
+        }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ------------------------------------
+    const int ew = warp - 2;
+    const int quarter = warp & 3;              // TMEM lane quarter this warp may touch
+    const int half = ew >> 2;                  // which half of the BN columns
+    const int row_in_tile = quarter * 32 + lane;
+    const int col0 = half * kColsPerThread;
+    int buf = 0; uint32_t tphase[2] = {0, 0}; bool ok = true;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    uint32_t epi_phase = 0;
+    // barrier over the 8 epilogue warps with a bounded wait (a plain bar.sync could
+    // hang if one warp had given up on an earlier wait)
+    auto epi_sync = [&]() -> bool {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(epi_bar);
+      const bool done = mbar_wait(epi_bar, epi_phase, abort_flag);
+      epi_phase ^= 1;
+      return done;
+    };
+
+    for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
+      const int tile = item / p.split_k, ks = item % p.split_k;
+      int pm, pn; tile_coords(tile, pm, pn);
+      const int row = pm * kBM + row_in_tile;
+      const int ncol0 = pn * BN + col0;
+      AccT acc[kColsPerThread];
+#pragma unroll
+      for (int i = 0; i < kColsPerThread; ++i) acc[i] = 0;
+
+      for (int kt = ks; kt < k_tiles_total && ok; kt += p.split_k) {
+        if (!mbar_wait(tfull_bar(buf), tphase[buf], abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t t_addr = tmem_base + lane_addr + (uint32_t)(buf * BN + col0);
+#pragma unroll
+        for (int c = 0; c < kColsPerThread / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld32(t_addr + c * 32, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float f = __uint_as_float(v[i]);
+            if constexpr (ACC64) {
+              acc[c * 32 + i] += float_to_fixed<64>(f, p.scale);
+            } else {
+              acc[c * 32 + i] += (p.int_bits == 16) ? (int32_t)float_to_fixed<16>(f, p.scale)
+                                                    : float_to_fixed<32>(f, p.scale);
+            }
+          }
+          if (p.partials && row < p.M) {
+            float* dst = p.partials + ((int64_t)kt * p.M + row) * p.N + ncol0 + c * 32;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (ncol0 + c * 32 + i < p.N) dst[i] = __uint_as_float(v[i]);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(buf));
+        tphase[buf] ^= 1; buf ^= 1;
+      }
+      if (!ok) break;
+
+      // ---- tile epilogue ----
+      const bool row_ok = row < p.M;
+      if (p.split_k > 1) {
+        // integer atomics are commutative: arrival order cannot change the sum
+        if (row_ok) {
+          if (p.int_bits == 64) {
+            unsigned long long* dst = (unsigned long long*)p.acc_scratch + (int64_t)row * p.N + ncol0;
+#pragma unroll
+            for (int i = 0; i < kColsPerThread; ++i)
+              if (ncol0 + i < p.N) atomicAdd(dst + i, (unsigned long long)(long long)acc[i]);
+          } else {
+            int* dst = (int*)p.acc_scratch + (int64_t)row * p.N + ncol0;
+#pragma unroll
+            for (int i = 0; i < kColsPerThread; ++i)
+              if (ncol0 + i < p.N) atomicAdd(dst + i, (int)acc[i]);
+          }
+        }
+        __threadfence();
+        // all 8 epilogue warps must have added before the tile counts as arrived
+        if (!epi_sync()) { ok = false; break; }
+        if (threadIdx.x == 64) *s_last = (atomicAdd(p.locks + tile, 1) == p.split_k - 1) ? 1 : 0;
+        if (!epi_sync()) { ok = false; break; }
+        const bool last = *s_last != 0;
+        if (last) {
+          __threadfence();
+          if (row_ok) {
+            if (p.int_bits == 64) {
+              long long* src = (long long*)p.acc_scratch + (int64_t)row * p.N + ncol0;
+#pragma unroll
+              for (int i = 0; i < kColsPerThread; ++i)
+                if (ncol0 + i < p.N) { acc[i] = (AccT)__ldcg(src + i); src[i] = 0; }
+            } else {
+              int* src = (int*)p.acc_scratch + (int64_t)row * p.N + ncol0;
+#pragma unroll
+              for (int i = 0; i < kColsPerThread; ++i)
+                if (ncol0 + i < p.N) { acc[i] = (AccT)__ldcg(src + i); src[i] = 0; }
+            }
+          }
+          if (threadIdx.x == 64) p.locks[tile] = 0;
+        }
+        if (!epi_sync()) { ok = false; break; }   // s_last may be rewritten only after everyone read it
+        if (!last) continue;
+      }
+      if (!row_ok) continue;
+
+      if (p.c_int) {
+        if (p.int_bits == 64) {
+          long long* dst = (long long*)p.c_int + (int64_t)row * p.N + ncol0;
+#pragma unroll
+          for (int i = 0; i < kColsPerThread; ++i) if (ncol0 + i < p.N) dst[i] = (long long)acc[i];
+        } else if (p.int_bits == 32) {
+          int32_t* dst = (int32_t*)p.c_int + (int64_t)row * p.N + ncol0;
+#pragma unroll
+          for (int i = 0; i < kColsPerThread; ++i) if (ncol0 + i < p.N) dst[i] = (int32_t)acc[i];
+        } else {
+          int16_t* dst = (int16_t*)p.c_int + (int64_t)row * p.N + ncol0;
+#pragma unroll
+          for (int i = 0; i < kColsPerThread; ++i) if (ncol0 + i < p.N) dst[i] = (int16_t)acc[i];
+        }
+      }
+      if (p.c) {
+        T* dst = (T*)p.c + (int64_t)row * p.c_sm + ncol0;
+        const T* bias = (const T*)p.bias;
+#pragma unroll
+        for (int g = 0; g < kColsPerThread / 8; ++g) {
+          alignas(16) T out[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int col = ncol0 + g * 8 + i;
+            long long q = (long long)acc[g * 8 + i];
+            if (!ACC64 && p.int_bits == 16) q = (long long)(int16_t)q;
+            float v = fixed_to_float<long long>(q, p.inv_scale);
+            if (bias && col < p.N) v = __fadd_rn(v, to_f32<T>(bias[col]));
+            out[i] = from_f32<T>(v);
+          }
+          const int colg = ncol0 + g * 8;
+          if (p.c_vec_ok && colg + 8 <= p.N) {
+            *reinterpret_cast<uint4*>(dst + g * 8) = *reinterpret_cast<const uint4*>(out);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) if (colg + i < p.N) dst[g * 8 + i] = out[i];
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------ teardown ----------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // let copies that are still in flight land before shared memory is released
+    const long long t0 = clock64();
+    while (clock64() - t0 < 200000) { __nanosleep(1000); }
+    if (threadIdx.x == 0 && p.status) atomicExch(p.status, FXPR_ERR_TIMEOUT);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)ptr;
+  }
+  return fn;
+}
+
+// 2-D row-major tensor [rows, cols] (cols contiguous), box [box_rows, 64 cols], 128 B swizzle.
+static bool make_map(CUtensorMap* m, int dtype, const void* base, int64_t rows, int64_t cols,
+                     int64_t row_stride_elems, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)row_stride_elems * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, dtype == FXPR_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                  2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+static int device_sms() {
+  static int cached[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (!cached[dev]) {
+    int n = 0, major = 0;
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    cached[dev] = (major == 10 && n > 0) ? n : -1;
+  }
+  return cached[dev];
+}
+
+bool gemm_tc_supported(const GemmArgs& g) {
+  if (g.dtype != FXPR_F16 && g.dtype != FXPR_BF16) return false;
+  if (g.K < 1 || g.k_tile < 64 || g.k_tile % 64 != 0) return false;
+  if (g.a_sk != 1 || (g.a_sm % 8) != 0 || ((uintptr_t)g.a & 15)) return false;
+  const bool b_nmajor = (g.b_sn == 1) && (g.b_sk % 8 == 0) && g.b_sk >= g.N;
+  const bool b_kmajor = (g.b_sk == 1) && (g.b_sn % 8 == 0) && g.b_sn >= g.K;
+  if (!(b_nmajor || b_kmajor) || ((uintptr_t)g.b & 15)) return false;
+  // very small problems stay on the CUDA-core kernel; the rule looks at N and K only
+  if (g.N < 64 || g.K < 64) return false;
+  return true;
+}
+
+int64_t gemm_tc_scratch_bytes(int64_t M, int64_t N, int int_bits) {
+  const int64_t acc = M * N * (int_bits == 64 ? 8 : 4);
+  const int64_t locks = ((M + kBM - 1) / kBM) * ((N + 127) / 128) * 4;
+  return ((acc + 255) / 256) * 256 + ((locks + 255) / 256) * 256;
+}
+
+template <typename T, int BN, bool ACC64, int STAGES>
+static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, TcParams& p, int sms, cudaStream_t s) {
+  using L = SmemLayout<BN, STAGES>;
+  auto k = gemm_tc_kernel<T, BN, ACC64, STAGES>;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
+    if (e != cudaSuccess) { set_last_error("gemm_tc smem attribute", e); return FXPR_ERR_CUDA; }
+    attr_done = true;
+  }
+  p.tiles_m = (p.M + kBM - 1) / kBM;
+  p.tiles_n = (p.N + BN - 1) / BN;
+  const int64_t items = (int64_t)p.tiles_m * p.tiles_n * p.split_k;
+  const int grid = (int)(items < sms ? items : sms);
+  k<<<grid, kThreads, L::kTotal, s>>>(ma, mb, p);
+  return check_launch("gemm_tc");
+}
+
+int gemm_tc(const GemmArgs& g, cudaStream_t s) {
+  const int sms = device_sms();
+  if (sms < 0) return FXPR_ERR_ARCH;
+  const bool b_kmajor = !((g.b_sn == 1) && (g.b_sk % 8 == 0));
+  const bool acc64 = g.int_bits == 64;
+  const int BN = acc64 ? 128 : 256;
+
+  CUtensorMap ma, mb;
+  if (!make_map(&ma, g.dtype, g.a, g.M, g.K, g.a_sm, kBM)) {
+    set_last_error("cuTensorMapEncodeTiled(A)", cudaErrorInvalidValue);
+    return FXPR_ERR_CUDA;
+  }
+  const bool okb = b_kmajor ? make_map(&mb, g.dtype, g.b, g.N, g.K, g.b_sn, 64)
+                            : make_map(&mb, g.dtype, g.b, g.K, g.N, g.b_sk, 64);
+  if (!okb) {
+    set_last_error("cuTensorMapEncodeTiled(B)", cudaErrorInvalidValue);
+    return FXPR_ERR_CUDA;
+  }
+
+  TcParams p;
+  p.bias = g.bias; p.c = g.c; p.c_int = g.c_int; p.partials = g.partials;
+  p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K; p.c_sm = g.c_sm;
+  p.k_tile = g.k_tile; p.int_bits = g.int_bits;
+  p.scale = (float)(1ull << g.frac_bits); p.inv_scale = 1.0f / p.scale;
+  p.b_kmajor = b_kmajor ? 1 : 0;
+  p.idesc = make_idesc(g.dtype == FXPR_BF16 ? 1 : 0, b_kmajor ? 0 : 1, BN, kBM);
+  p.c_vec_ok = (g.c && (((uintptr_t)g.c & 15) == 0) && (g.c_sm % 8 == 0)) ? 1 : 0;
+  p.status = g.status;
+  const int k_tiles = (int)((g.K + g.k_tile - 1) / g.k_tile);
+  p.split_k = g.split_k < 1 ? 1 : (g.split_k > k_tiles ? k_tiles : g.split_k);
+  p.acc_scratch = nullptr; p.locks = nullptr;
+  if (p.split_k > 1) {
+    const int64_t need = gemm_tc_scratch_bytes(g.M, g.N, g.int_bits);
+    if (!g.scratch || g.scratch_bytes < need) return FXPR_ERR_SCRATCH;
+    if ((uintptr_t)g.scratch & 15) return FXPR_ERR_BAD_ARG;
+    const int64_t acc_bytes = ((g.M * g.N * (g.int_bits == 64 ? 8 : 4) + 255) / 256) * 256;
+    p.acc_scratch = g.scratch;
+    p.locks = (int32_t*)((char*)g.scratch + acc_bytes);
+  }
+
+  if (g.dtype == FXPR_BF16) {
+    return acc64 ? launch_tc<__nv_bfloat16, 128, true, 6>(ma, mb, p, sms, s)
+                 : launch_tc<__nv_bfloat16, 256, false, 4>(ma, mb, p, sms, s);
+  }
+  return acc64 ? launch_tc<__half, 128, true, 6>(ma, mb, p, sms, s)
+               : launch_tc<__half, 256, false, 4>(ma, mb, p, sms, s);
+}
+
+}  // namespace fxpr

@@ -264,6 +264,31 @@ def _get_gemm_scratch(device: torch.device, nbytes: int) -> torch.Tensor:
     return cur
 
 
+_status_words: dict[int, torch.Tensor] = {}
+
+
+def _status_word(device: torch.device) -> torch.Tensor:
+    """Per-device int32 the kernels set when a bounded device-side wait gives up."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    t = _status_words.get(idx)
+    if t is None:
+        t = torch.zeros(1, device=device, dtype=torch.int32)
+        _status_words[idx] = t
+    return t
+
+
+def check_device_status(device=None) -> None:
+    """Synchronise and raise if any kernel reported a timed-out wait since the
+    last check (not on the hot path: tests, benchmarks and debugging call it)."""
+    for idx, t in list(_status_words.items()):
+        if device is not None and torch.device(device).index not in (None, idx):
+            continue
+        v = int(t.item())
+        if v != 0:
+            t.zero_()
+            nat.check(v, f"device status word on cuda:{idx}")
+
+
 _SM_COUNT: dict[int, int] = {}
 
 
@@ -329,7 +354,7 @@ def _gemm_common(a, b, bias, int_bits, frac_bits, want_c: bool, want_int: bool):
             nat.DTYPE_CODE[a.dtype], M, N, K, a.stride(0), a.stride(1), b.stride(0), b.stride(1),
             c.stride(0) if c is not None else N, int_bits, frac_bits, k_tile, split_k, flags,
             nat.ptr(scratch), scratch_bytes, nat.ptr(partials if partials is not None and partials.numel() else None),
-            nat.stream_ptr(a.device))
+            _status_word(a.device).data_ptr(), nat.stream_ptr(a.device))
     nat.check(st, "gemm_fxp")
     return c, c_int
 
