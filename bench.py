@@ -1,0 +1,373 @@
+#!/usr/bin/env python
+"""Benchmark of the fixed-point reduction hot path on B200.
+
+``python bench.py --gpus N --steps K --warmup W`` prints ONE JSON line.  A step
+is one pass of the headline kernel -- the fixed-point GEMM of the benchmark
+configuration (A [4096,4096] ~N(0,1) x B [4096,4096] ~N(0,0.02), bf16, fp32 MMA
+partials per K-tile of 64 rounded to Q16.16 and summed in int64, bf16 out) --
+over one synthetic batch.  ``value`` is TFLOP/s with inputs resident in HBM,
+``e2e`` the same through ``torch.ops.fxpr.gemm_fxp`` with pinned host buffers and
+the host<->device copies inside the timed region.  The other configurations
+(RMSNorm, decode/prefill attention, log-softmax) are timed briefly and reported
+under ``others``.  With N > 1 every rank runs an independent replica (the
+kernels have no exchange step): weak scaling, no collective in the data path.
+
+``--impl reference`` times the CPU restatement of the reference's algorithm
+(the torch int64 emulation in ``oracle/``; the reference itself has no CPU path
+and its Triton kernels cannot run without a GPU) on the host cores, on a bounded
+row-sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+PKG = ROOT / "vllm-triton-fixed-point-reductions_b200"
+for _p in (str(ROOT), str(PKG)):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+
+METRIC = "fxp GEMM TFLOP/s + split-K decode attn GB/s (% roofline); bitwise-invariant Y/N"
+GEMM = dict(M=4096, N=4096, K=4096, k_tile=64, int_bits=64, frac_bits=16)
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+NOMINAL = {"hbm_gbs": 8000.0, "bf16_tflops": 2250.0}
+
+
+def load_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            d = json.loads(p.read_text())
+            return {k: float(d[k]) for k in FALLBACK_PEAKS if k in d} | {"source": "measured"}
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons through NVML (read-only queries) in a
+    background thread while a timed region runs."""
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+               0x4: "sw_power_cap"}
+
+    def __init__(self, index: int, period_s: float = 0.01):
+        self.index, self.period = index, period_s
+        self.samples: list[tuple[int, int]] = []
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._err = None
+
+    def _run(self):
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            idx = self.index
+            if visible:
+                try:
+                    idx = int(visible.split(",")[self.index])
+                except (ValueError, IndexError):
+                    idx = self.index
+            h = pynvml.nvmlDeviceGetHandleByIndex(idx)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
+            while not self._stop.is_set():
+                mhz = pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)
+                try:
+                    rs = pynvml.nvmlDeviceGetCurrentClocksEventReasons(h)
+                except Exception:
+                    rs = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                self.samples.append((mhz, rs))
+                time.sleep(self.period)
+        except Exception as e:  # NVML missing: report, do not fail the benchmark
+            self._err = repr(e)
+
+    def start(self):
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+        time.sleep(0.05)
+
+    def stop(self):
+        self._stop.set()
+        if self._thread:
+            self._thread.join(timeout=2)
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "samples": 0,
+                    "reasons": [f"no samples: {self._err}"]}
+        mask = 0
+        for _, rs in self.samples:
+            mask |= rs
+        return {"sm_mhz": statistics.median(m for m, _ in self.samples),
+                "sm_max_mhz": self.max_mhz, "samples": len(self.samples),
+                "reasons": sorted(n for b, n in self.REASONS.items() if mask & b)}
+
+
+def time_cuda(fn, steps: int, warmup: int, dist=None) -> float:
+    """Seconds for `steps` calls of fn (device time via CUDA events on the current
+    stream), after `warmup` untimed calls; max over ranks."""
+    for i in range(warmup):
+        fn(i)
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        fn(warmup + i)
+    e1.record()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    sec = e0.elapsed_time(e1) / 1e3
+    if dist is not None:
+        t = torch.tensor([sec], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        sec = float(t.item())
+    return sec
+
+
+# ------------------------------------------------------------------------------
+# CPU baseline (oracle) on a bounded sample of the GEMM workload
+# ------------------------------------------------------------------------------
+
+def cpu_gemm_baseline(rows: int, repeats: int = 1):
+    from oracle import fxp_oracle as orc
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    g = torch.Generator().manual_seed(1)
+    a = torch.randn((rows, GEMM["K"]), generator=g).to(torch.bfloat16)
+    b = (0.02 * torch.randn((GEMM["K"], GEMM["N"]), generator=g)).to(torch.bfloat16)
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        orc.gemm_fxp(a, b, None, GEMM["int_bits"], GEMM["frac_bits"], k_tile=GEMM["k_tile"])
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    flops = 2.0 * rows * GEMM["N"] * GEMM["K"]
+    return {"value": flops / best / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
+            "kind": "port",
+            "sample": f"{rows} of {GEMM['M']} rows of A against the full B, {best:.2f} s "
+                      f"(torch CPU int64 emulation of the Q16.16 path)"}
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps, warm = max(1, args.steps), max(0, args.warmup)
+    rows = 256
+    for _ in range(min(warm, 1)):
+        cpu_gemm_baseline(64)
+    vals = [cpu_gemm_baseline(rows) for _ in range(min(steps, 5))]
+    best = max(vals, key=lambda d: d["value"])
+    ms = 2.0 * rows * GEMM["N"] * GEMM["K"] / (best["value"] * 1e12) * 1e3
+    line = {
+        "impl": "reference", "metric": METRIC, "value": best["value"], "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": min(steps, 5), "warmup": min(warm, 1), "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": "cfg1 fxp GEMM bf16 4096x4096x4096, K-tile 64, Q16.16 int64 "
+                               "(CPU arm: row sample)", **GEMM},
+        "cpu_baseline": best,
+        "e2e": {"value": best["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "note": "reference has no CPU path of its own (CUDA-only Triton kernels); this is the "
+                "torch CPU restatement of its algorithm from oracle/",
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------
+
+def run_gpu_arm(args):
+    import fxpr_vllm  # noqa: F401
+    from fxpr_vllm import _lib as L
+    from fxpr_vllm import synthetic as syn
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist_mod.init_process_group("nccl", device_id=dev)
+        dist = dist_mod
+    peaks = load_peaks()
+    steps, warm = max(1, args.steps), max(3, args.warmup)
+    M, N, K = GEMM["M"], GEMM["N"], GEMM["K"]
+    flops = 2.0 * M * N * K
+
+    # inputs larger than L2: rotate over 4 independent (A, B) sets = 268 MB + outputs
+    nsets = 4
+    sets = [syn.gemm_inputs(M, N, K, torch.bfloat16, seed=1 + i, device=dev) for i in range(nsets)]
+    outs = [None] * nsets
+
+    def gemm_step(i):
+        a, b = sets[i % nsets]
+        outs[i % nsets] = torch.ops.fxpr.gemm_fxp(a, b, None, GEMM["int_bits"], GEMM["frac_bits"])
+
+    sampler = ClockSampler(local)
+    with L.overrides(gemm_k_tile=GEMM["k_tile"], gemm_split_k=1):
+        # bitwise invariance: split-K sweep and repeats on set 0
+        a0, b0 = sets[0]
+        ref = torch.ops.fxpr.gemm_fxp(a0, b0, None, 64, 16)
+        invariant = True
+        for sk in (1, 2, 4, 8, 16):
+            with L.overrides(gemm_split_k=sk):
+                for _ in range(2):
+                    invariant &= bool(torch.equal(ref, torch.ops.fxpr.gemm_fxp(a0, b0, None, 64, 16)))
+        sampler.start()
+        sec = time_cuda(gemm_step, steps, warm, dist)
+        clocks = sampler.stop()
+        L.check_device_status()
+
+        # end to end through the public op with pinned host buffers
+        ha, hb = sets[0][0].cpu().pin_memory(), sets[0][1].cpu().pin_memory()
+        hc = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+
+        def e2e_step(i):
+            da = ha.to(dev, non_blocking=True)
+            db = hb.to(dev, non_blocking=True)
+            c = torch.ops.fxpr.gemm_fxp(da, db, None, GEMM["int_bits"], GEMM["frac_bits"])
+            hc.copy_(c, non_blocking=True)
+
+        e2e_steps = max(3, min(steps, 10))
+        sec_e2e = time_cuda(e2e_step, e2e_steps, 3, dist)
+    e2e_ok = bool(torch.equal(hc, ref.cpu()))
+
+    value = world * flops * steps / sec / 1e12
+    per_gpu = flops * steps / sec / 1e12
+    peak = peaks["bf16_tflops"]
+    line = {
+        "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
+        "warmup": warm, "ms_per_step": sec / steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "cfg1 fxp GEMM bf16 4096x4096x4096, K-tile 64, Q16.16 int64, "
+                               "bf16 out (replica per GPU)", **GEMM,
+                   "l2": f"rotating {nsets} input sets (268 MB) > 126 MB L2",
+                   "seed": "1..4"},
+        "bitwise_invariant": "Y" if invariant else "N",
+        "invariance_checked": "split-K {1,2,4,8,16} x 2 repeats, identical bf16 outputs",
+        "e2e": {"value": world * flops * e2e_steps / sec_e2e / 1e12, "unit": "TFLOP/s",
+                "h2d_bytes_per_step": ha.numel() * 2 + hb.numel() * 2,
+                "d2h_bytes_per_step": hc.numel() * 2, "matches_resident_run": e2e_ok},
+        "gpu_launches": steps,
+        "clocks": clocks,
+        "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peak, "unit": "TFLOP/s",
+                     "frac": per_gpu / peak, "traffic": None,
+                     "peak_source": f"{peaks['source']} cuBLAS bf16 burst",
+                     "frac_of_nominal_2250": per_gpu / NOMINAL["bf16_tflops"],
+                     "algorithmic": "2*M*N*K = 137.44 GFLOP per launch"},
+    }
+    if not args.skip_others:
+        line["others"] = bench_others(dev, peaks, L, syn)
+    if rank == 0:
+        if not args.skip_cpu:
+            line["cpu_baseline"] = cpu_gemm_baseline(256)
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def bench_others(dev, peaks, L, syn):
+    """Short timings of the other configurations (device time, L2 flushed by rotating
+    inputs where they are smaller than L2)."""
+    res = {}
+    hbm = peaks["hbm_gbs"]
+
+    def t(fn, steps=10, warm=3):
+        return time_cuda(fn, steps, warm) / steps
+
+    # cfg0: RMSNorm + residual, fp32 [2048, 4096]
+    sets = [syn.rms_norm_inputs(seed=10 + i, device=dev) for i in range(4)]
+    sec = t(lambda i: torch.ops.fxpr.rms_norm_fxp_residual(*sets[i % 4][:2], sets[i % 4][2], 1e-6))
+    byts = 4 * 2048 * 4096 * 4 + 4096 * 4
+    res["rms_norm_residual_cfg0"] = {"us": sec * 1e6, "GB/s": byts / sec / 1e9,
+                                     "frac_hbm_measured": byts / sec / 1e9 / hbm}
+
+    # cfg3b: log-softmax fp32 [256, 128256]
+    lsets = [syn.logits_inputs(seed=20 + i, device=dev) for i in range(2)]
+    sec = t(lambda i: torch.ops.fxpr.log_softmax_fxp(lsets[i % 2], 16))
+    byts = 2 * 256 * 128256 * 4
+    res["log_softmax_cfg3b"] = {"us": sec * 1e6, "GB/s": byts / sec / 1e9,
+                                "frac_hbm_measured": byts / sec / 1e9 / hbm}
+
+    # casts: fp32 -> int64 -> fp32 on [2048, 4096]
+    x = sets[0][0]
+    sec = t(lambda i: torch.ops.fxpr.float_to_fixed(sets[i % 4][0], 64, 16))
+    byts = x.numel() * 12
+    res["float_to_fixed_i64"] = {"us": sec * 1e6, "GB/s": byts / sec / 1e9,
+                                 "frac_hbm_measured": byts / sec / 1e9 / hbm}
+
+    # cfg2: paged decode attention, batch 64, ctx U[512, 8192]
+    lens = syn.decode_batch_lens()
+    q, kv, qsl, sl, bt = syn.paged_attention_inputs(lens, [1] * len(lens), device=dev)
+    o = torch.empty_like(q)
+    byts = sum(lens) * 4096 + 2 * q.numel() * 2
+    dec = {}
+    ref = None
+    inv = True
+    for splits in (1, 4, 8, 16):
+        def step(i, s=splits):
+            torch.ops.fxpr.unified_attention_fxp(q, kv, o, qsl, sl, bt, 1, None, True, None, 64, 16,
+                                                 0.0, 0, s)
+        sec = t(step, steps=5, warm=2)
+        dec[f"splits{splits}"] = {"us": sec * 1e6, "GB/s": byts / sec / 1e9,
+                                  "frac_hbm_measured": byts / sec / 1e9 / hbm}
+        cur = o.clone()
+        if ref is None:
+            ref = cur
+        inv &= bool(torch.equal(ref, cur))
+    dec["bitwise_invariant"] = "Y" if inv else "N"
+    dec["algorithmic_bytes"] = byts
+    res["decode_attention_cfg2"] = dec
+
+    # cfg3a: varlen causal prefill, 16 seqs U[128, 4096]
+    plens = syn.prefill_batch_lens()
+    q, kv, qsl, sl, bt = syn.paged_attention_inputs(plens, plens, device=dev, seed=6)
+    o = torch.empty_like(q)
+    fl = 8192.0 * sum(l * (l + 1) for l in plens)
+
+    def pstep(i):
+        torch.ops.fxpr.unified_attention_fxp(q, kv, o, qsl, sl, bt, max(plens), None, True, None, 64,
+                                             16, 0.0, 0, 1)
+    sec = t(pstep, steps=3, warm=1)
+    res["prefill_attention_cfg3a"] = {"ms": sec * 1e3, "TFLOP/s": fl / sec / 1e12,
+                                      "frac_tensor_measured": fl / sec / 1e12 / peaks["bf16_tflops"]}
+    L.check_device_status()
+    return res
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-others", action="store_true")
+    ap.add_argument("--skip-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -182,11 +182,13 @@ def rms_norm(
         x2 = xf
     sq = xf * xf
     acc = float_to_fixed(sq, 64, frac_bits).sum(dim=-1, keepdim=True)
-    total = acc.to(torch.float32) * (1.0 / float(1 << frac_bits))
-    mean = torch.clamp(total / torch.tensor(float(h), dtype=torch.float32), min=0.0)
-    rrms = torch.tensor(1.0, dtype=torch.float32) / torch.sqrt(
-        mean + torch.tensor(eps, dtype=torch.float32)
-    )
+    # The per-row scalar chain runs in numpy: its float32 divide and sqrt are
+    # correctly rounded, whereas torch's vectorised CPU sqrt is not (a few results
+    # per thousand are off by one ulp) and torch divides by a scalar as x * (1/s).
+    total = (acc.to(torch.float32) * (1.0 / float(1 << frac_bits))).numpy()
+    mean = np.maximum(total / np.float32(h), np.float32(0.0)).astype(np.float32)
+    rrms_np = (np.float32(1.0) / np.sqrt((mean + np.float32(eps)).astype(np.float32))).astype(np.float32)
+    rrms = torch.from_numpy(rrms_np)
     y = (x2 * weight.to(torch.float32)) * rrms
     y = y.to(dt).reshape(x.shape)
     if new_res is not None:
