@@ -162,6 +162,41 @@ int fxpr_attention(const void* q, const void* k_cache, const void* v_cache, void
                    void* scratch, int64_t scratch_bytes, int32_t* status_word,
                    void* stream);
 
+/*
+ * fxpr_attention for callers that cannot allocate device memory.  It has no
+ * counterpart in the reference (whose launcher allocates scratch with torch on
+ * every call).  Same arguments as fxpr_attention without scratch/scratch_bytes:
+ * the split path's scratch lives in a fixed device array inside the library,
+ * fxpr_attention_static_scratch_capacity() bytes (4 MiB) on every GPU that
+ * loads the library, held until the process exits.  Meant for hosts with no
+ * allocator on this path: a server that gave all of HBM to its KV cache, a C
+ * caller without torch, a loop that must avoid cudaMalloc's implicit
+ * synchronisation.  It calls no cudaMalloc/cudaFree and no allocating library.
+ *   - Problems whose scratch need (fxpr_attention_scratch_bytes) exceeds the
+ *     capacity are refused with FXPR_ERR_SCRATCH and a message in
+ *     fxpr_last_error(); nothing is launched.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current); make that first call
+ *     before any stream capture.
+ *   - All calls share the one array and it keeps the previous call's contents;
+ *     each call clears what must start at zero on the given stream.  Two calls
+ *     whose kernels can overlap on the GPU (different streams) race on it:
+ *     serialise them.
+ */
+int64_t fxpr_attention_static_scratch_capacity(void);
+int fxpr_attention_static_scratch(
+                   const void* q, const void* k_cache, const void* v_cache, void* o,
+                   const int32_t* query_start_loc, const int32_t* seq_lens,
+                   const int32_t* block_table, const float* alibi,
+                   int dtype, int64_t total_q_tokens, int num_reqs, int num_heads,
+                   int num_kv_heads, int head_dim, int page_size,
+                   int64_t q_st, int64_t q_sh, int64_t o_st, int64_t o_sh,
+                   int64_t kv_sblock, int64_t kv_sslot, int64_t kv_shead,
+                   int64_t bt_stride, int max_query_len, int flags,
+                   double softmax_scale, double logit_softcap, int window,
+                   int int_bits, int frac_bits, int num_splits,
+                   int32_t* status_word, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -13,6 +13,10 @@ void set_last_error(const char* what, cudaError_t err) {
            cudaGetErrorString(err), cudaGetErrorName(err));
 }
 
+void set_last_error_text(const char* text) {
+  snprintf(g_last_error, sizeof(g_last_error), "%s", text);
+}
+
 // Launch errors are reported without synchronising: only configuration errors
 // (bad grid, too much shared memory, no kernel image) surface here, which is what
 // a caller inside a CUDA-graph capture can still act on.

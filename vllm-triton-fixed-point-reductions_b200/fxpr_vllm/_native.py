@@ -56,6 +56,11 @@ SIGNATURES = {
                             _i, _i64, _i, _i, _i, _i, _i,
                             _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64,
                             _i, _i, _d, _d, _i, _i, _i, _i, _vp, _i64, _vp, _vp]),
+    "fxpr_attention_static_scratch_capacity": (_i64, []),
+    "fxpr_attention_static_scratch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
+                                           _i, _i64, _i, _i, _i, _i, _i,
+                                           _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64,
+                                           _i, _i, _d, _d, _i, _i, _i, _i, _vp, _vp]),
 }
 
 _lib = None
