@@ -201,3 +201,49 @@ def test_tp_sharding_single_gpu_equals_unsharded():
         assert torch.equal(acc, full)
     out = torch.ops.fxpr.gemm_fxp_epilogue(full, None, torch.bfloat16, 16)
     assert torch.equal(out, _gemm(a, b, None, 64, 16))
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("int_bits", [32, 64])
+@pytest.mark.parametrize("kt,split", [(64, 1), (128, 1), (64, 3), (128, 2)])
+def test_fast_epilogue_equals_plain_conversion_with_outliers(dtype, int_bits, kt, split):
+    """The magic-number epilogue with its exact fix-up gives the same integers as the
+    tensor-core kernel that converts every partial with cvt.rni (saturating), including
+    rows whose partials leave the fast range, saturate int32 or overflow the 32-bit sum."""
+    from fxpr_vllm import _native as nat
+
+    M, N, K = 300, 520, 1096
+    a = _rand((M, K), dtype, 101).cuda()
+    b = _rand((K, N), dtype, 102, 0.05).cuda()
+    a[3, :] = 900.0
+    a[M - 1, 5::7] = -3000.0
+    a[M // 2, :64] = 6.0e4
+    a[7, 100] = float("inf") if int_bits == 32 else 5.0e4
+    with L.overrides(gemm_k_tile=kt, gemm_split_k=split):
+        fast_i = torch.ops.fxpr.gemm_fxp_int(a, b, int_bits, 16)
+        fast_c = _gemm(a, b, None, int_bits, 16)
+    with L.overrides(gemm_k_tile=kt, gemm_split_k=1, gemm_flags=nat.GEMM_FORCE_EXACT_TC):
+        exact_i = torch.ops.fxpr.gemm_fxp_int(a, b, int_bits, 16)
+        exact_c = _gemm(a, b, None, int_bits, 16)
+    assert torch.equal(fast_i, exact_i)
+    assert torch.equal(fast_c.view(torch.int16), exact_c.view(torch.int16))
+    L.check_device_status()
+
+
+@pytest.mark.parametrize("int_bits,frac", [(16, 8), (64, 32), (32, 8)])
+def test_tensor_core_route_other_q_formats(int_bits, frac):
+    a = _rand((130, 512), torch.bfloat16, 111, 0.3).cuda()
+    b = _rand((512, 264), torch.bfloat16, 112, 0.1).cuda()
+    got = torch.ops.fxpr.gemm_fxp_int(a, b, int_bits, frac).cpu().to(torch.int64)
+    exp = orc.gemm_fxp(a.cpu(), b.cpu(), None, int_bits, frac, return_int=True)
+    tol = 4 if frac <= 16 else 4 * 2 ** (frac - 16)
+    assert (got - exp).abs().max().item() <= tol
+
+
+def test_b_given_as_transposed_weight_view():
+    # weight kept (N, K) and passed as .t(): the K-major operand path, no transpose copy
+    a = _rand((200, 1024), torch.bfloat16, 121).cuda()
+    w = _rand((384, 1024), torch.bfloat16, 122, 0.05).cuda()
+    v1 = torch.ops.fxpr.gemm_fxp_int(a, w.t(), 64, 16)
+    v2 = torch.ops.fxpr.gemm_fxp_int(a, w.t().contiguous(), 64, 16)
+    assert torch.equal(v1, v2)

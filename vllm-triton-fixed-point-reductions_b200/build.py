@@ -48,7 +48,8 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     nvcc = _nvcc()
     OBJ.mkdir(exist_ok=True)
     LIB.parent.mkdir(exist_ok=True)
-    headers = sorted(CSRC.glob("*.cuh")) + sorted((ROOT.parent / "include").glob("*.h"))
+    headers = (sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.inl"))
+               + sorted((ROOT.parent / "include").glob("*.h")))
     sources = sorted(CSRC.glob("*.cu"))
     jobs = []
     for src in sources:

@@ -41,7 +41,7 @@ extern "C" int fxpr_gemm(const void* a, const void* b, const void* bias, void* c
   g.dtype = dtype; g.M = M; g.N = N; g.K = K;
   g.a_sm = a_sm; g.a_sk = a_sk; g.b_sk = b_sk; g.b_sn = b_sn; g.c_sm = c_sm;
   g.int_bits = int_bits; g.frac_bits = frac_bits; g.k_tile = k_tile; g.split_k = split_k;
-  g.scratch = scratch; g.scratch_bytes = scratch_bytes; g.status = status_word;
+  g.scratch = scratch; g.scratch_bytes = scratch_bytes; g.status = status_word; g.flags = flags;
 
   if (!(flags & FXPR_GEMM_FORCE_PORTABLE) && gemm_tc_supported(g)) return gemm_tc(g, s);
   return gemm_portable(a, b, bias, c, c_int, partials_out, dtype, M, N, K, a_sm, a_sk, b_sk, b_sn,

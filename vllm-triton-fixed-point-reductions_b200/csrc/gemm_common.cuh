@@ -10,7 +10,7 @@ struct GemmArgs {
   const void* a; const void* b; const void* bias; void* c; void* c_int; float* partials;
   int dtype; int64_t M, N, K; int64_t a_sm, a_sk, b_sk, b_sn, c_sm;
   int int_bits, frac_bits, k_tile, split_k;
-  void* scratch; int64_t scratch_bytes; int32_t* status;
+  void* scratch; int64_t scratch_bytes; int32_t* status; int flags;
 };
 
 // Tensor-core (tcgen05 / TMEM / TMA) kernel.

@@ -25,146 +25,13 @@
 
 #include "fxp_common.cuh"
 #include "gemm_common.cuh"
+#include "tc_common.cuh"
 
 namespace fxpr {
-
-static constexpr int kBM = 128;           // tile rows = TMEM lanes
-static constexpr int kBK = 64;            // smem stage depth: 64 x 2 B = one 128-byte swizzle row
-static constexpr int kEpiWarps = 8;
-static constexpr int kThreads = (2 + kEpiWarps) * 32;
-static constexpr int kGroupM = 8;
-static constexpr long long kWaitCycles = 4000000000LL;  // ~2 s at 2 GHz
-
-// ---------------------------------------------------------------------------------
-// PTX wrappers
-// ---------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  return ok;
-}
-// Bounded wait.  Returns false when the wait gave up or another thread aborted.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  int spins = 0;
-  while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 63) == 0) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitCycles) { *abort_flag = 1; return false; }
-    }
-  }
-  return true;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
-                                            int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() {
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_after() {
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
-                                         uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_wait_ld() {
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// Shared-memory matrix descriptor (sm_100 format): start address, leading / stride
-// byte offsets (all >> 4), version 1, 128-byte swizzle.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-  uint64_t d = 0;
-  d |= (uint64_t)((addr & 0x3ffff) >> 4);
-  d |= (uint64_t)((lbo_bytes >> 4) & 0x3fff) << 16;
-  d |= (uint64_t)((sbo_bytes >> 4) & 0x3fff) << 32;
-  d |= (uint64_t)1 << 46;   // descriptor version (sm_100)
-  d |= (uint64_t)2 << 61;   // SWIZZLE_128B
-  return d;
-}
-
-// Instruction descriptor for kind::f16: fp32 accumulate, A/B format (0 = f16, 1 = bf16),
-// A K-major, B major-ness selectable, N >> 3 at bit 17, M >> 4 at bit 24.
-__host__ __device__ inline uint32_t make_idesc(int ab_format, int b_mn_major, int n, int m) {
-  uint32_t d = 0;
-  d |= 1u << 4;                         // D format = f32
-  d |= (uint32_t)ab_format << 7;        // A format
-  d |= (uint32_t)ab_format << 10;       // B format
-  d |= (uint32_t)(b_mn_major ? 1 : 0) << 16;
-  d |= (uint32_t)(n >> 3) << 17;
-  d |= (uint32_t)(m >> 4) << 24;
-  return d;
-}
 
 // ---------------------------------------------------------------------------------
 // kernel
 // ---------------------------------------------------------------------------------
-struct TcParams {
-  const void* bias; void* c; void* c_int; float* partials;
-  void* acc_scratch; int32_t* locks; int32_t* status;
-  int M, N, K; int64_t c_sm;
-  int k_tile, split_k, int_bits; float scale, inv_scale;
-  int tiles_m, tiles_n; uint32_t idesc; int b_kmajor; int c_vec_ok;
-};
-
-template <int BN, int STAGES>
-struct SmemLayout {
-  static constexpr int kABytes = kBM * kBK * 2;
-  static constexpr int kBBytes = BN * kBK * 2;
-  static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kBarOffset = STAGES * kStageBytes;
-  static constexpr int kTotal = kBarOffset + 256 + 1024;  // barriers + alignment slack
-};
-
 template <typename T, int BN, bool ACC64, int STAGES>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
@@ -255,6 +122,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     // ------------------------------ MMA issuer ----------------------------------
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0; int buf = 0; uint32_t tphase[2] = {0, 0}; bool ok = true;
+      // A: K-major, 8-row groups 1024 B apart, +32 B per 16-wide k step.  B K-major: same.
+      // B N-major: 64-column slabs 8192 B apart (leading offset), 8-k-row groups 1024 B
+      // apart, +2048 B per 16-deep k step.
+      const uint64_t adesc0 = make_smem_desc(smem_base, 16, 1024);
+      const uint64_t bdesc0 = p.b_kmajor ? make_smem_desc(smem_base + L::kABytes, 16, 1024)
+                                         : make_smem_desc(smem_base + L::kABytes, 8192, 1024);
+      const uint64_t b_kstep = p.b_kmajor ? 2 : 128;
+      constexpr uint64_t kStageStep = L::kStageBytes >> 4;
+      const uint32_t idesc = p.idesc;
       for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
         const int ks = item % p.split_k;
         for (int kt = ks; kt < k_tiles_total && ok; kt += p.split_k) {
@@ -264,18 +140,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           for (int ch = 0; ch < chunks; ++ch) {
             if (!mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
             tc_fence_after();
-            const uint32_t sa = smem_base + stage * L::kStageBytes;
-            const uint32_t sb = sa + L::kABytes;
-#pragma unroll
-            for (int k = 0; k < kBK / 16; ++k) {
-              // A: K-major, 8-row groups 1024 B apart, +32 B per 16-wide k step
-              const uint64_t adesc = make_smem_desc(sa + k * 32, 16, 1024);
-              // B K-major: same as A.  B N-major: 64-column slabs 8192 B apart (leading
-              // offset), 8-k-row groups 1024 B apart, +2048 B per 16-deep k step
-              const uint64_t bdesc = p.b_kmajor ? make_smem_desc(sb + k * 32, 16, 1024)
-                                                : make_smem_desc(sb + k * 2048, 8192, 1024);
-              umma_f16(d_tmem, adesc, bdesc, p.idesc, (ch | k) ? 1u : 0u);
-            }
+            // descriptors differ from stage 0 / k 0 only in the 14-bit address field
+            const uint64_t ad = adesc0 + (uint64_t)stage * kStageStep;
+            const uint64_t bd = bdesc0 + (uint64_t)stage * kStageStep;
+            umma_f16(d_tmem, ad, bd, idesc, ch ? 1u : 0u);
+            umma_f16(d_tmem, ad + 2, bd + b_kstep, idesc, 1u);
+            umma_f16(d_tmem, ad + 4, bd + 2 * b_kstep, idesc, 1u);
+            umma_f16(d_tmem, ad + 6, bd + 3 * b_kstep, idesc, 1u);
             umma_commit(empty_bar(stage));   // frees the smem stage when these MMAs finish
             if (++stage == STAGES) { stage = 0; phase ^= 1; }
           }
@@ -473,7 +344,7 @@ static EncodeTiledFn get_encode_fn() {
 }
 
 // 2-D row-major tensor [rows, cols] (cols contiguous), box [box_rows, 64 cols], 128 B swizzle.
-static bool make_map(CUtensorMap* m, int dtype, const void* base, int64_t rows, int64_t cols,
+bool tc_make_map(CUtensorMap* m, int dtype, const void* base, int64_t rows, int64_t cols,
                      int64_t row_stride_elems, int box_rows) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return false;
@@ -488,7 +359,7 @@ static bool make_map(CUtensorMap* m, int dtype, const void* base, int64_t rows, 
   return r == CUDA_SUCCESS;
 }
 
-static int device_sms() {
+int tc_device_sms() {
   static int cached[64] = {0};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -538,20 +409,24 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, TcParams& p, 
   return check_launch("gemm_tc");
 }
 
+bool gemm_tc_fast_supported(const GemmArgs& g, int split_k);
+int gemm_tc_fast(const GemmArgs& g, TcParams& p, const CUtensorMap& ma, const CUtensorMap& mb,
+                 int bn, cudaStream_t s);
+
 int gemm_tc(const GemmArgs& g, cudaStream_t s) {
-  const int sms = device_sms();
+  const int sms = tc_device_sms();
   if (sms < 0) return FXPR_ERR_ARCH;
   const bool b_kmajor = !((g.b_sn == 1) && (g.b_sk % 8 == 0));
   const bool acc64 = g.int_bits == 64;
   const int BN = acc64 ? 128 : 256;
 
   CUtensorMap ma, mb;
-  if (!make_map(&ma, g.dtype, g.a, g.M, g.K, g.a_sm, kBM)) {
+  if (!tc_make_map(&ma, g.dtype, g.a, g.M, g.K, g.a_sm, kBM)) {
     set_last_error("cuTensorMapEncodeTiled(A)", cudaErrorInvalidValue);
     return FXPR_ERR_CUDA;
   }
-  const bool okb = b_kmajor ? make_map(&mb, g.dtype, g.b, g.N, g.K, g.b_sn, 64)
-                            : make_map(&mb, g.dtype, g.b, g.K, g.N, g.b_sk, 64);
+  const bool okb = b_kmajor ? tc_make_map(&mb, g.dtype, g.b, g.N, g.K, g.b_sn, 64)
+                            : tc_make_map(&mb, g.dtype, g.b, g.K, g.N, g.b_sk, 64);
   if (!okb) {
     set_last_error("cuTensorMapEncodeTiled(B)", cudaErrorInvalidValue);
     return FXPR_ERR_CUDA;
@@ -576,6 +451,10 @@ int gemm_tc(const GemmArgs& g, cudaStream_t s) {
     const int64_t acc_bytes = ((g.M * g.N * (g.int_bits == 64 ? 8 : 4) + 255) / 256) * 256;
     p.acc_scratch = g.scratch;
     p.locks = (int32_t*)((char*)g.scratch + acc_bytes);
+  }
+
+  if (!(g.flags & FXPR_GEMM_FORCE_EXACT_TC) && gemm_tc_fast_supported(g, p.split_k)) {
+    return gemm_tc_fast(g, p, ma, mb, (g.flags & FXPR_GEMM_TILE_N256) ? 256 : 128, s);
   }
 
   if (g.dtype == FXPR_BF16) {

@@ -94,6 +94,7 @@ class _Overrides(threading.local):
     gemm_portable: bool = False
     attn_portable: bool = False
     gemm_partials: bool = False
+    gemm_flags: int = 0
     last_partials: torch.Tensor | None = None
 
 
@@ -102,10 +103,11 @@ _ovr = _Overrides()
 
 @contextlib.contextmanager
 def overrides(*, gemm_k_tile=None, gemm_split_k=None, gemm_portable=None,
-              attn_portable=None, gemm_partials=None):
+              attn_portable=None, gemm_partials=None, gemm_flags=None):
     """Temporarily pin kernel-selection knobs (K-tile, split-K, portable route)."""
-    names = ("gemm_k_tile", "gemm_split_k", "gemm_portable", "attn_portable", "gemm_partials")
-    vals = (gemm_k_tile, gemm_split_k, gemm_portable, attn_portable, gemm_partials)
+    names = ("gemm_k_tile", "gemm_split_k", "gemm_portable", "attn_portable", "gemm_partials",
+             "gemm_flags")
+    vals = (gemm_k_tile, gemm_split_k, gemm_portable, attn_portable, gemm_partials, gemm_flags)
     old = {n: getattr(_ovr, n) for n in names}
     try:
         for n, v in zip(names, vals):
@@ -334,7 +336,7 @@ def _gemm_common(a, b, bias, int_bits, frac_bits, want_c: bool, want_int: bool):
     if not split_k:
         split_k = pick_split_k(M, N, K, k_tile, int_bits, _sm_count(a.device))
     split_k = max(1, min(split_k, -(-K // k_tile) if K else 1))
-    flags = nat.GEMM_FORCE_PORTABLE if _ovr.gemm_portable else 0
+    flags = (nat.GEMM_FORCE_PORTABLE if _ovr.gemm_portable else 0) | int(_ovr.gemm_flags)
     lib = nat.load()
     scratch = None
     scratch_bytes = 0

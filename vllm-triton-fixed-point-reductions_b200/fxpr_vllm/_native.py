@@ -31,6 +31,8 @@ DTYPE_CODE = {
 }
 
 GEMM_FORCE_PORTABLE = 1
+GEMM_FORCE_EXACT_TC = 2
+GEMM_CHECK_SUMSQ = 4
 ATTN_CAUSAL = 1
 ATTN_FORCE_PORTABLE = 2
 
