@@ -95,6 +95,10 @@ extern "C" int fxpr_attention(const void* q, const void* k_cache, const void* v_
   p.inv_scale = 1.0f / p.scale;
   p.partial_max = nullptr; p.total_denom = nullptr; p.total_wv = nullptr; p.locks = nullptr;
 
+  // The tensor-core route merges its splits through distributed shared memory and needs
+  // no scratch; only the CUDA-core route uses the caller's buffer.
+  if (!(flags & FXPR_ATTN_FORCE_PORTABLE) && attention_mma_supported(p, dtype))
+    return attention_mma(p, dtype, max_query_len, s);
   if (num_splits > 1) {
     const AttnScratchLayout l = attn_scratch_layout(total_q_tokens, num_heads, head_dim, num_splits);
     if (!scratch || scratch_bytes < l.total) return FXPR_ERR_SCRATCH;
@@ -108,7 +112,5 @@ extern "C" int fxpr_attention(const void* q, const void* k_cache, const void* v_
     if (e != cudaSuccess) { set_last_error("attention scratch memset", e); return FXPR_ERR_CUDA; }
   }
 
-  if (!(flags & FXPR_ATTN_FORCE_PORTABLE) && attention_mma_supported(p, dtype))
-    return attention_mma(p, dtype, max_query_len, s);
   return attention_portable(p, dtype, s);
 }

@@ -1,0 +1,151 @@
+// Kernel and launcher of the tensor-core attention route (included by attention_mma.cu).
+//
+// Template: T = io dtype, HD = head size (64 | 128), NW = warps per CTA (16 query rows
+// each), STASH = keep this CTA's fp32 scores in shared memory between the two passes
+// (decode), ACC64 = 64-bit integer accumulators.
+// Grid: x = KV split (= rank in the cluster), y = q_block * num_kv_heads + kv_head,
+// z = request.
+
+template <typename T, int HD, int NW, bool STASH, bool ACC64>
+__global__ void __launch_bounds__(NW * 32)
+attn_mma_kernel(const AttnParams p, const MmaAttnShape sh) {
+  constexpr int RC = HD / 8;                       // 16-byte chunks per K/V/Q row
+  constexpr int BM = 16 * NW;                      // query rows per CTA
+  constexpr int NT = NW * 32;
+  constexpr int kTileBytes = kTileN * HD * 2;
+  constexpr int kStageBytes = STASH ? kTileBytes : 2 * kTileBytes;   // K | K+V
+  constexpr int NSTAGE = STASH ? 3 : 2;
+  using AccT = typename IntOf<ACC64 ? 64 : 32>::type;
+
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint8_t* q_s = smem;                                            // BM x HD io elements
+  uint8_t* stage_s = q_s + BM * HD * 2;                           // NSTAGE stages
+  float* rmax_s = reinterpret_cast<float*>(stage_s + NSTAGE * kStageBytes);       // [BM]
+  long long* den_s = reinterpret_cast<long long*>(rmax_s + BM);                   // [BM]
+  float* stash_s = reinterpret_cast<float*>(den_s + BM);                          // decode only
+  long long* wv_s = reinterpret_cast<long long*>(stage_s);        // [BM][HD], reuses the stages
+
+  cg::cluster_group cluster = cg::this_cluster();
+  const int S = gridDim.x;
+  const int rank = blockIdx.x;
+  const int hkv = p.num_kv_heads;
+  const int qb = blockIdx.y / hkv, kvh = blockIdx.y % hkv;
+  const int req = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+
+  const int q_start = p.qsl[req], q_len = p.qsl[req + 1] - q_start;
+  const int G = sh.rows_per_token;
+  const int tok0 = qb * sh.tokens_per_block;
+  if (tok0 >= q_len) return;                       // same decision in every CTA of the cluster
+  const int seq_len = p.seq_lens[req];
+  const int ctx = seq_len - q_len;
+  const int tok_end = min(q_len, tok0 + sh.tokens_per_block);
+  const int32_t* bt = p.block_table + (int64_t)req * p.bt_stride;
+
+  // ---- key range of this row block, dealt to the cluster ranks in whole tiles ----------
+  const int hi_key = p.causal ? min(seq_len, ctx + tok_end) : seq_len;
+  const int lo_key = p.window > 0 ? max(0, ctx + tok0 - p.window + 1) : 0;
+  const int t_first = lo_key / kTileN;
+  const int t_last = max(t_first, (hi_key + kTileN - 1) / kTileN);
+  const int per_rank = (t_last - t_first + S - 1) / S;
+  const int t0 = min(t_last, t_first + rank * per_rank);
+  const int t1 = min(t_last, t0 + per_rank);
+
+  // the stash is sized from the block table's width on the host; never index past it
+  if (STASH && per_rank * kTileN > sh.stash_keys) return;
+
+  // ---- the two rows this thread owns in the MMA accumulator layout ------------------
+  int r_tok[2], r_head[2], r_kend[2], r_kbeg[2]; bool r_valid[2]; float r_slope[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = warp * 16 + g + 8 * h;
+    r_tok[h] = tok0 + r / G;
+    r_head[h] = kvh * G + r % G;
+    r_valid[h] = r_tok[h] < q_len;
+    const int pos = ctx + r_tok[h];
+    r_kend[h] = p.causal ? min(seq_len, pos + 1) : seq_len;
+    r_kbeg[h] = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    r_slope[h] = (p.alibi && r_valid[h]) ? p.alibi[r_head[h]] : 0.0f;
+    if (!r_valid[h]) { r_kend[h] = 0; r_kbeg[h] = 0; }
+  }
+
+  // ---- Q rows -> shared memory (zero rows beyond the block's tokens) ----------------------
+  for (int idx = threadIdx.x; idx < BM * RC; idx += NT) {
+    const int r = idx / RC, c = idx % RC;
+    const int tok = tok0 + r / G;
+    const bool v = tok < q_len;
+    const T* src = (const T*)p.q + (int64_t)(q_start + (v ? tok : 0)) * p.q_st +
+                   (int64_t)(kvh * G + r % G) * p.q_sh + c * 8;
+    cp_async16(smem_addr(q_s) + swz<RC>(r, c), src, v);
+  }
+  cp_async_commit();
+
+  const T* kbase = (const T*)p.k + (int64_t)kvh * p.kv_shead;
+  const T* vbase = (const T*)p.v + (int64_t)kvh * p.kv_shead;
+  const int pages_per_tile = kTileN / 16;          // block-table entries are looked up per 16 keys
+
+  // stage one 64-key tile of K or V: 16-byte cp.async per (key, chunk); rows past the
+  // sequence are zero-filled and never touch the block table
+  auto issue_tile = [&](const T* base, int t, uint32_t dst) {
+    int64_t page_off[4];
+#pragma unroll
+    for (int q4 = 0; q4 < pages_per_tile; ++q4) {
+      const int n = t * kTileN + q4 * 16;
+      page_off[q4] = (n < seq_len) ? (int64_t)bt[n / p.page_size] * p.kv_sblock +
+                                         (int64_t)(n % p.page_size) * p.kv_sslot
+                                   : -1;
+    }
+#pragma unroll
+    for (int it = 0; it < kTileN * RC / NT; ++it) {
+      const int idx = threadIdx.x + it * NT;
+      const int key = idx / RC, c = idx % RC;
+      const int n = t * kTileN + key;
+      const bool v = n < seq_len;
+      const int64_t po = page_off[key >> 4];
+      const T* src = v ? base + po + (int64_t)(key & 15) * p.kv_sslot + c * 8 : base;
+      cp_async16(dst + swz<RC>(key, c), src, v);
+    }
+  };
+
+  const uint32_t stage0 = smem_addr(stage_s);
+  const uint32_t qs_addr = smem_addr(q_s);
+  const float ninf = -__int_as_float(0x7f800000);
+
+  // scores of one tile for this warp's 16 rows: s[j][e], j = 8-key group, e = C-fragment slot
+  auto qk_tile = [&](uint32_t k_addr, int t, float (&s)[8][4]) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f; }
+#pragma unroll
+    for (int kk2 = 0; kk2 < HD / 32; ++kk2) {
+      uint32_t a0[4], a1[4];
+      ldsm_x4(qs_addr + swz<RC>(warp * 16 + (lane & 15), kk2 * 4 + (lane >> 4)), a0[0], a0[1], a0[2], a0[3]);
+      ldsm_x4(qs_addr + swz<RC>(warp * 16 + (lane & 15), kk2 * 4 + 2 + (lane >> 4)), a1[0], a1[1], a1[2], a1[3]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4(k_addr + swz<RC>(j * 8 + (lane & 7), kk2 * 4 + (lane >> 3)), b0, b1, b2, b3);
+        mma16816<T>(s[j], a0, b0, b1);
+        mma16816<T>(s[j], a1, b2, b3);
+      }
+    }
+    // scale to log2 space, soft-cap, ALiBi, masks (attention.py:103-121, 249-254)
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int h = e >> 1;
+        const int n = t * kTileN + j * 8 + 2 * t4 + (e & 1);
+        float v = __fmul_rn(s[j][e], p.ss_log2);
+        if (p.cap_log2 > 0.0f) v = __fmul_rn(p.cap_log2, tanhf(__fdiv_rn(v, p.cap_log2)));
+        if (p.alibi) v = __fadd_rn(v, __fmul_rn(r_slope[h], __fsub_rn((float)n, (float)(ctx + r_tok[h]))));
+        s[j][e] = (n >= r_kbeg[h] && n < r_kend[h]) ? v : ninf;
+      }
+  };
+
+  const int srows = sh.stash_rows;                 // rows kept in the stash: <= 8, or 16
+  const int slanes = srows <= 8 ? 4 * srows : 32;
+  const int svals = srows <= 8 ? 2 : 4;
+
+#include "attention_mma_passes.inl"
+}
