@@ -24,7 +24,6 @@ import json
 import os
 import statistics
 import sys
-import threading
 import time
 from pathlib import Path
 
@@ -53,64 +52,56 @@ def load_peaks():
     return dict(FALLBACK_PEAKS, source="fallback")
 
 
-class ClockSampler:
-    """Samples SM clocks and throttle reasons through NVML (read-only queries) in a
-    background thread while a timed region runs."""
+def sample_clocks_under_load(fn, index: int, seconds: float = 1.5):
+    """Run `fn` back to back for `seconds` while polling SM clock and throttle reasons
+    with nvidia-smi (a separate process; polling NVML in-process at a high rate was seen to
+    stall kernel launches, so the timed region itself is never sampled)."""
+    import subprocess
 
-    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
-               0x4: "sw_power_cap"}
-
-    def __init__(self, index: int, period_s: float = 0.01):
-        self.index, self.period = index, period_s
-        self.samples: list[tuple[int, int]] = []
-        self.max_mhz = None
-        self._stop = threading.Event()
-        self._thread = None
-        self._err = None
-
-    def _run(self):
+    q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+    visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+    gpu_id = str(index)
+    if visible:
+        ids = visible.split(",")
+        if index < len(ids):
+            gpu_id = ids[index]
+    try:
+        proc = subprocess.Popen(["nvidia-smi", f"--id={gpu_id}", f"--query-gpu={q}",
+                                 "--format=csv,noheader,nounits", "-lms", "100"],
+                                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+    except Exception as exc:
+        return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [f"nvidia-smi unavailable: {exc!r}"]}
+    t_end = time.time() + seconds
+    i = 0
+    while time.time() < t_end:
+        for _ in range(20):
+            fn(i)
+            i += 1
+        torch.cuda.synchronize()
+    proc.terminate()
+    try:
+        out, _ = proc.communicate(timeout=3)
+    except Exception:
+        proc.kill()
+        out = ""
+    sm, mx, reasons = [], [], set()
+    names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+    for ln in out.splitlines():
+        f = [x.strip() for x in ln.split(",")]
+        if len(f) < 6:
+            continue
         try:
-            import pynvml
-
-            pynvml.nvmlInit()
-            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
-            idx = self.index
-            if visible:
-                try:
-                    idx = int(visible.split(",")[self.index])
-                except (ValueError, IndexError):
-                    idx = self.index
-            h = pynvml.nvmlDeviceGetHandleByIndex(idx)
-            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
-            while not self._stop.is_set():
-                mhz = pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)
-                try:
-                    rs = pynvml.nvmlDeviceGetCurrentClocksEventReasons(h)
-                except Exception:
-                    rs = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h)
-                self.samples.append((mhz, rs))
-                time.sleep(self.period)
-        except Exception as e:  # NVML missing: report, do not fail the benchmark
-            self._err = repr(e)
-
-    def start(self):
-        self._thread = threading.Thread(target=self._run, daemon=True)
-        self._thread.start()
-        time.sleep(0.05)
-
-    def stop(self):
-        self._stop.set()
-        if self._thread:
-            self._thread.join(timeout=2)
-        if not self.samples:
-            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "samples": 0,
-                    "reasons": [f"no samples: {self._err}"]}
-        mask = 0
-        for _, rs in self.samples:
-            mask |= rs
-        return {"sm_mhz": statistics.median(m for m, _ in self.samples),
-                "sm_max_mhz": self.max_mhz, "samples": len(self.samples),
-                "reasons": sorted(n for b, n in self.REASONS.items() if mask & b)}
+            sm.append(float(f[0])); mx.append(float(f[1]))
+        except ValueError:
+            continue
+        for n, v in zip(names, f[2:6]):
+            if v.lower().startswith("active"):
+                reasons.add(n)
+    return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+            "samples": len(sm), "reasons": sorted(reasons),
+            "window": f"{seconds} s of back-to-back steps right after the timed region"}
 
 
 def time_cuda(fn, steps: int, warmup: int, dist=None) -> float:
@@ -222,7 +213,6 @@ def run_gpu_arm(args):
         a, b = sets[i % nsets]
         outs[i % nsets] = torch.ops.fxpr.gemm_fxp(a, b, None, GEMM["int_bits"], GEMM["frac_bits"])
 
-    sampler = ClockSampler(local)
     with L.overrides(gemm_k_tile=GEMM["k_tile"], gemm_split_k=1):
         # bitwise invariance: split-K sweep and repeats on set 0
         a0, b0 = sets[0]
@@ -232,9 +222,8 @@ def run_gpu_arm(args):
             with L.overrides(gemm_split_k=sk):
                 for _ in range(2):
                     invariant &= bool(torch.equal(ref, torch.ops.fxpr.gemm_fxp(a0, b0, None, 64, 16)))
-        sampler.start()
         sec = time_cuda(gemm_step, steps, warm, dist)
-        clocks = sampler.stop()
+        clocks = sample_clocks_under_load(gemm_step, local)
         L.check_device_status()
 
         # end to end through the public op with pinned host buffers
@@ -323,12 +312,12 @@ def bench_others(dev, peaks, L, syn):
     dec = {}
     ref = None
     inv = True
-    for splits in (1, 4, 8, 16):
+    for splits in (0, 1, 4, 8, 16):
         def step(i, s=splits):
             torch.ops.fxpr.unified_attention_fxp(q, kv, o, qsl, sl, bt, 1, None, True, None, 64, 16,
                                                  0.0, 0, s)
         sec = t(step, steps=5, warm=2)
-        dec[f"splits{splits}"] = {"us": sec * 1e6, "GB/s": byts / sec / 1e9,
+        dec["auto" if splits == 0 else f"splits{splits}"] = {"us": sec * 1e6, "GB/s": byts / sec / 1e9,
                                   "frac_hbm_measured": byts / sec / 1e9 / hbm}
         cur = o.clone()
         if ref is None:

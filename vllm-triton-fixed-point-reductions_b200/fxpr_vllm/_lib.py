@@ -420,6 +420,31 @@ def pick_num_splits(requested, num_requests, num_q_blocks, num_heads, num_kv_til
     return _next_pow2(split) if split >= 2 else 1
 
 
+def _tensor_core_route(q, kv_cache, num_heads, num_kv_heads, head_dim, page_size) -> bool:
+    """Mirror of the C side's routing rule (dtype / geometry only, never batch)."""
+    g = num_heads // num_kv_heads
+    return (q.dtype in (torch.float16, torch.bfloat16) and head_dim in (64, 128)
+            and page_size % 16 == 0 and g in (1, 2, 4, 8, 16) and not _ovr.attn_portable)
+
+
+def pick_num_splits_b200(requested, num_requests, max_query_len, num_heads, num_kv_heads,
+                         max_keys, num_sms):
+    """Split policy of the tensor-core route, where splits are cluster ranks: results do
+    not depend on it, so it only balances the GPU.  Decode keeps each CTA's key slice near
+    1024 keys (small score stash -> more resident CTAs); prefill splits only when the row
+    blocks alone cannot fill the SMs.  Host shapes only, so it is fixed under a CUDA graph."""
+    if requested >= 1:
+        return min(requested, 16)
+    g = num_heads // num_kv_heads
+    if max_query_len * g <= 16:
+        return max(1, min(8, -(-max_keys // 1024)))
+    rows_per_block = 64
+    blocks = num_requests * num_kv_heads * max(1, -(-(max_query_len * g) // rows_per_block))
+    if blocks >= num_sms or max_keys <= 2048:
+        return 1
+    return max(1, min(8, num_sms // blocks))
+
+
 def unified_attention_fxp_run(q, kv_cache, o, query_start_loc, seq_lens, block_table,
                               max_query_len, alibi_slopes, is_causal, softmax_scale,
                               fxp_int_bits, fxp_frac_bits, logit_softcap, window_size,
@@ -461,8 +486,13 @@ def unified_attention_fxp_run(q, kv_cache, o, query_start_loc, seq_lens, block_t
     num_q_blocks = max(1, -(-max(1, int(max_query_len)) // block_m))
     max_kv_blocks = block_table.shape[1] if block_table.dim() == 2 else 0
     num_kv_tiles = -(-max(1, max_kv_blocks * page_size) // block_n)
-    splits = pick_num_splits(int(num_kv_splits), num_requests, num_q_blocks, num_heads,
-                             num_kv_tiles, _sm_count(q.device))
+    if _tensor_core_route(q, kv_cache, num_heads, num_kv_heads, head_dim, page_size):
+        splits = pick_num_splits_b200(int(num_kv_splits), num_requests, int(max_query_len),
+                                      num_heads, num_kv_heads, max(1, max_kv_blocks * page_size),
+                                      _sm_count(q.device))
+    else:
+        splits = pick_num_splits(int(num_kv_splits), num_requests, num_q_blocks, num_heads,
+                                 num_kv_tiles, _sm_count(q.device))
 
     lib = nat.load()
     scratch = None
