@@ -205,10 +205,10 @@ int attention_mma(const AttnParams& p_in, int dtype, int max_query_len, cudaStre
 #define FXPR_ATTN(TT, HDV)                                                                      \
   do {                                                                                          \
     if (small && stash && sh.stash_rows <= 8)                                                   \
-      return acc64 ? launch_decode<TT, HDV, HDV / 16, true, true>(p, sh, s)                     \
-                   : launch_decode<TT, HDV, HDV / 16, false, true>(p, sh, s);                   \
-    if (small && stash) return acc64 ? launch_decode<TT, HDV, HDV / 16, true, false>(p, sh, s)  \
-                                     : launch_decode<TT, HDV, HDV / 16, false, false>(p, sh, s);\
+      return acc64 ? launch_decode<TT, HDV, 4, true, true>(p, sh, s)                     \
+                   : launch_decode<TT, HDV, 4, false, true>(p, sh, s);                   \
+    if (small && stash) return acc64 ? launch_decode<TT, HDV, 4, true, false>(p, sh, s)  \
+                                     : launch_decode<TT, HDV, 4, false, false>(p, sh, s);\
     if (small) return acc64 ? launch_mma<TT, HDV, 1, false, true>(p, sh, s)                     \
                             : launch_mma<TT, HDV, 1, false, false>(p, sh, s);                   \
     return acc64 ? launch_mma<TT, HDV, 4, false, true>(p, sh, s)                                \

@@ -14,7 +14,7 @@
 // ROWS8: at most 8 of the 16 tile rows are real (e.g. one token x GQA group of 4): the
 // second half of every accumulator fragment is known to be masked and is skipped.
 template <typename T, int HD, int NW, bool ACC64, bool ROWS8>
-__global__ void __launch_bounds__(NW * 32, 1024 / (NW * 32))
+__global__ void __launch_bounds__(NW * 32, 4)
 attn_decode_kernel(const AttnParams p, const MmaAttnShape sh) {
   constexpr int RC = HD / 8;
   constexpr int NT = NW * 32;

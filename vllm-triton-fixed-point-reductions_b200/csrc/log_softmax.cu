@@ -7,11 +7,11 @@
 // absent); this is the order-free replacement for the float log_softmax of
 // vLLM's Sampler.compute_logprobs.
 //
-// A row is split over a thread-block cluster of 1..8 CTAs; each CTA keeps its
+// A row is split over a thread-block cluster of 1..16 CTAs; each CTA keeps its
 // slice in shared memory as fp32, so HBM is read once and written once.  The
 // row maximum and the integer sum are exchanged through distributed shared
 // memory (every CTA reads every peer's slot; max and integer add are order-free).
-// Rows too long for 8 x shared memory fall back to re-reading the slice.
+// Rows too long for 16 x shared memory fall back to re-reading the slice.
 #include <cooperative_groups.h>
 
 #include "fxp_common.cuh"
@@ -84,7 +84,14 @@ log_softmax_kernel(const T* __restrict__ x, float* __restrict__ y, int cols, int
     else acc += (unsigned long long)(long long)float_to_fixed<32>(e, scale);
   };
   if (CACHE) {
-    for (int i = threadIdx.x; i < len; i += blockDim.x) add_one(slice[i]);
+    // four independent exp chains per thread and iteration (the polynomial is a long
+    // dependent chain; integer addition makes the visiting order irrelevant)
+    const int n4 = len / 4;
+    for (int c = threadIdx.x; c < n4; c += blockDim.x) {
+      const float4 v = *reinterpret_cast<const float4*>(slice + c * 4);
+      add_one(v.x); add_one(v.y); add_one(v.z); add_one(v.w);
+    }
+    for (int i = n4 * 4 + threadIdx.x; i < len; i += blockDim.x) add_one(slice[i]);
   } else {
     for (int i = threadIdx.x; i < len; i += blockDim.x) add_one(to_f32<T>(xr[i]));
   }
@@ -127,14 +134,14 @@ template <typename T>
 static int launch_lsm(const void* x, float* y, int64_t rows, int cols, float scale, float inv,
                       bool wide_q, cudaStream_t s) {
   constexpr int V = 16 / sizeof(T);
-  // Smallest cluster whose slice fits comfortably (<= 64 KB keeps 3 CTAs per SM),
-  // else the smallest that fits at all, else 8 with re-reads.
   int csize = 1;
   auto slice_of = [&](int c) {
     int sl = (cols + c - 1) / c;
     return ((sl + 15) / 16) * 16;  // multiple of 16 elements: aligned for every dtype
   };
-  while (csize < 8 && (size_t)slice_of(csize) * 4 > 64 * 1024) csize *= 2;
+  // up to 16 CTAs per row (16 needs the non-portable cluster attribute): 32 KB slices
+  // keep ~6 CTAs resident per SM, so loads, exp work and stores of different rows overlap
+  while (csize < 16 && (size_t)slice_of(csize) * 4 > 32 * 1024) csize *= 2;
   int slice_len = slice_of(csize);
   const bool cache = (size_t)slice_len * 4 <= (size_t)kLsmMaxSliceBytes;
   const bool vec_ok = (cols % V == 0) && ((((uintptr_t)x) & 15) == 0);
@@ -163,6 +170,10 @@ static int launch_lsm(const void* x, float* y, int64_t rows, int cols, float sca
                                kLsmMaxSliceBytes);                                           \
       if (e != cudaSuccess) { set_last_error("log_softmax smem attribute", e); return FXPR_ERR_CUDA; } \
     }                                                                                        \
+    if (csize > 8) {                                                                         \
+      e = cudaFuncSetAttribute(k, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);        \
+      if (e != cudaSuccess) { set_last_error("log_softmax cluster attribute", e); return FXPR_ERR_CUDA; } \
+    }                                                                                        \
     e = cudaLaunchKernelEx(&cfg, k, xp, y, cols, slice_len, scale, inv, wide_q);             \
   } while (0)
   if (cache) {
@@ -184,7 +195,7 @@ extern "C" int fxpr_log_softmax(const void* x, int x_dtype, float* y, int64_t ro
   if (rows < 0 || cols < 0 || frac_bits < 0 || frac_bits > 32) return FXPR_ERR_BAD_ARG;
   if (rows == 0 || cols == 0) return FXPR_OK;
   if (!x || !y) return FXPR_ERR_BAD_ARG;
-  if (cols > (int64_t)1 << 30 || rows * 8 > 0x7fffffffLL) return FXPR_ERR_BAD_ARG;
+  if (cols > (int64_t)1 << 30 || rows * 16 > 0x7fffffffLL) return FXPR_ERR_BAD_ARG;
   const float scale = (float)(1ull << frac_bits);
   const float inv = 1.0f / scale;
   const bool wide_q = frac_bits > 30;
