@@ -93,8 +93,11 @@ int fxpr_log_softmax(const void* x, int x_dtype, float* y, int64_t rows,
                      int64_t cols, int frac_bits, void* stream);
 
 /*
- * Bytes of zero-initialised scratch fxpr_gemm needs for this problem
- * (0 when split_k <= 1).  The kernel leaves the scratch zeroed again.
+ * Bytes of scratch fxpr_gemm needs for this problem (0 when split_k <= 1):
+ * tile counters followed by one plane of integer partial tiles per split.
+ * The buffer must be zero-filled once before its first use; after that it may
+ * be reused, without clearing, for calls of any shape that it is large enough
+ * for (calls that share a buffer must be ordered on one stream).
  * Replaces _get_splitk_scratch, fxpr_vllm/_triton/gemm.py:86-107.
  */
 int64_t fxpr_gemm_scratch_bytes(int64_t M, int64_t N, int int_bits, int split_k);
@@ -107,7 +110,8 @@ int64_t fxpr_gemm_scratch_bytes(int64_t M, int64_t N, int int_bits, int split_k)
  * accumulators (for the tensor-parallel reduce and for tests).
  * k_tile: conversion granularity (0 = reference default: 128 for f16/bf16, 64
  * for f32).  split_k: 0/1 = none, else the K-tiles are dealt round-robin to
- * split_k CTAs per output tile and merged with integer atomics (needs scratch).
+ * split_k CTAs per output tile; each leaves an integer partial tile in the
+ * scratch and the last to arrive adds them up (order-free, needs scratch).
  * partials_out: optional fp32 [ceil(K/k_tile), M, N] dump of the per-tile
  * float partials (tests only; must be NULL when split_k > 1).
  * status_word: optional device int the tensor-core kernel sets to

@@ -1,0 +1,133 @@
+"""Outputs of the reference plugin's own Triton kernels, recorded on a B200 by
+``tests/golden/make_reference_fixtures.py``, against the oracle (CPU) and against this
+library's kernels (GPU).
+
+Casts are integer work and must agree bit for bit.  For the GEMM and the attention the
+reference's float partial products come out of ``tl.dot`` whose in-tile summation order
+is the tensor core's, so the recorded outputs may differ from a sequential-k evaluation
+in the last place of the io dtype on a small fraction of elements; the bounds below are
+"at most one unit in the last place, on at most 2 % of the elements"."""
+from __future__ import annotations
+
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+sys.path.insert(0, str(Path(__file__).resolve().parent / "golden"))
+import reference_cases as rc  # noqa: E402
+
+from oracle import fxp_oracle as oracle  # noqa: E402
+
+FIX = Path(__file__).resolve().parent / "golden" / "reference_b200.pt"
+FLOAT_BITS = {torch.float16: 16, torch.float32: 32, torch.float64: 64}
+
+
+@pytest.fixture(scope="module")
+def ref():
+    return torch.load(FIX, weights_only=True)
+
+
+def ulp_distance(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """Distance in representable values between two tensors of one 16/32-bit float dtype."""
+    it = {2: torch.int16, 4: torch.int32}[a.element_size()]
+    def key(t):
+        i = t.contiguous().view(it).to(torch.int64)
+        sign = 1 << (8 * t.element_size() - 1)
+        return torch.where(i < 0, -(i + sign) - 0, i)   # monotonic in the float's value
+    return (key(a) - key(b)).abs()
+
+
+def last_place_distance(got, want, quanta=4, frac_bits=16):
+    """Units in the last place, except that differences of a few Q-format quanta count as
+    one unit: near zero the io dtype is finer than the fixed-point grid."""
+    d = ulp_distance(got, want)
+    small = (got.double() - want.double()).abs() <= quanta * 2.0 ** -frac_bits
+    return torch.where(small, d.clamp(max=1), d)
+
+
+def assert_last_place(got, want, what, max_frac=0.02, max_ulp=1, quanta=4):
+    assert got.dtype == want.dtype and got.shape == want.shape, what
+    d = last_place_distance(got, want, quanta)
+    assert int(d.max()) <= max_ulp, f"{what}: {int(d.max())} ulp"
+    frac = float((d != 0).float().mean())
+    assert frac <= max_frac, f"{what}: {frac:.4f} of the elements differ"
+
+
+# ------------------------------------------------------------------ oracle (CPU)
+def test_oracle_casts_match_reference_bits(ref):
+    for name, x, bits, frac in rc.cast_cases():
+        q = oracle.float_to_fixed(x, bits, frac)
+        assert torch.equal(q, ref[name]["q"]), name
+        assert torch.equal(oracle.fixed_to_float(q, FLOAT_BITS[x.dtype], frac), ref[name]["back"]), name
+
+
+def test_oracle_gemm_matches_reference_to_last_place(ref):
+    for name, a, b, bias, bits in rc.gemm_cases():
+        c = oracle.gemm_fxp(a, b, bias, bits, 16, k_tile=128)
+        assert_last_place(c, ref[name]["c"], name)
+
+
+def test_oracle_attention_matches_reference_to_last_place(ref):
+    for name, q, kv, qsl, sl, bt, mq, bits, splits in rc.attention_cases():
+        o = oracle.attention_fxp(q, kv, qsl, sl, bt, is_causal=True, int_bits=bits, frac_bits=16)
+        # every 64-key tile contributes its own rounding to the Q-format grid
+        assert_last_place(o, ref[name]["o"], name, quanta=8)
+
+
+def test_oracle_rms_norm_close_to_reference(ref):
+    # the reference sums squares in fp32 (order-dependent); the integer sum agrees to fp32 rounding
+    # (a row whose 1/rms differs in the last place differs everywhere, hence no fraction bound)
+    for name, x, r, w in rc.rms_cases():
+        y, rn = oracle.rms_norm(x, w, 1e-6, residual=r)
+        assert torch.equal(rn, ref[name]["r"]), name
+        assert_last_place(y, ref[name]["y"], name, max_frac=1.0)
+
+
+# ------------------------------------------------------------------ this library (GPU)
+@pytest.mark.gpu
+def test_gpu_casts_match_reference_bits(ref):
+    import fxpr_vllm  # noqa: F401
+    for name, x, bits, frac in rc.cast_cases():
+        q = torch.ops.fxpr.float_to_fixed(x.cuda(), bits, frac)
+        assert torch.equal(q.cpu(), ref[name]["q"]), name
+        back = torch.ops.fxpr.fixed_to_float(q, FLOAT_BITS[x.dtype], frac)
+        assert torch.equal(back.cpu(), ref[name]["back"]), name
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("portable", [False, True])
+def test_gpu_gemm_matches_reference_to_last_place(ref, portable):
+    import fxpr_vllm
+    from fxpr_vllm import _lib
+    for name, a, b, bias, bits in rc.gemm_cases():
+        with _lib.overrides(gemm_k_tile=128, gemm_portable=portable):
+            c = torch.ops.fxpr.gemm_fxp(a.cuda(), b.cuda(), None if bias is None else bias.cuda(), bits, 16)
+        assert_last_place(c.cpu(), ref[name]["c"], name)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("portable", [False, True])
+def test_gpu_attention_matches_reference_to_last_place(ref, portable):
+    import fxpr_vllm
+    from fxpr_vllm import _lib
+    for name, q, kv, qsl, sl, bt, mq, bits, splits in rc.attention_cases():
+        o = torch.empty_like(q, device="cuda")
+        with _lib.overrides(attn_portable=portable):
+            torch.ops.fxpr.unified_attention_fxp(q.cuda(), kv.cuda(), o, qsl.cuda(), sl.cuda(), bt.cuda(),
+                                                 mq, None, True, None, bits, 16, 0.0, 0, splits)
+        # the tensor-core route rounds the weights to the io dtype before P.V and uses
+        # ex2.approx: allow one more unit there
+        assert_last_place(o.cpu(), ref[name]["o"], name, max_frac=0.02 if portable else 0.25,
+                          max_ulp=1 if portable else 2, quanta=8)
+
+
+@pytest.mark.gpu
+def test_gpu_rms_norm_close_to_reference(ref):
+    import fxpr_vllm  # noqa: F401
+    for name, x, r, w in rc.rms_cases():
+        rd = r.cuda().clone()
+        y = torch.ops.fxpr.rms_norm_fxp_residual(x.cuda(), rd, w.cuda(), 1e-6)
+        assert torch.equal(rd.cpu(), ref[name]["r"]), name
+        assert_last_place(y.cpu(), ref[name]["y"], name, max_frac=1.0)

@@ -16,7 +16,7 @@ static int default_k_tile(int dtype) {
 
 extern "C" int64_t fxpr_gemm_scratch_bytes(int64_t M, int64_t N, int int_bits, int split_k) {
   if (split_k <= 1 || M <= 0 || N <= 0) return 0;
-  return gemm_tc_scratch_bytes(M, N, int_bits);
+  return gemm_tc_scratch_bytes(M, N, int_bits, split_k);
 }
 
 extern "C" int fxpr_gemm(const void* a, const void* b, const void* bias, void* c, void* c_int,

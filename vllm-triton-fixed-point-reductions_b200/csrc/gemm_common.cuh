@@ -16,7 +16,7 @@ struct GemmArgs {
 // Tensor-core (tcgen05 / TMEM / TMA) kernel.
 bool gemm_tc_supported(const GemmArgs& g);
 int gemm_tc(const GemmArgs& g, cudaStream_t s);
-int64_t gemm_tc_scratch_bytes(int64_t M, int64_t N, int int_bits);
+int64_t gemm_tc_scratch_bytes(int64_t M, int64_t N, int int_bits, int split_k);
 
 // CUDA-core kernel (any dtype / strides).
 int gemm_portable(const void* a, const void* b, const void* bias, void* c, void* c_int,

@@ -221,22 +221,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       // ---- tile epilogue ----
       const bool row_ok = row < p.M;
       if (p.split_k > 1) {
-        // integer atomics are commutative: arrival order cannot change the sum
-        if (row_ok) {
-          if (p.int_bits == 64) {
-            unsigned long long* dst = (unsigned long long*)p.acc_scratch + (int64_t)row * p.N + ncol0;
+        // Every split leaves its integer partial tile in its own plane of the scratch,
+        // column-major inside the tile (a warp's 32 rows are 32 consecutive words); the
+        // split that arrives last adds the other planes to its registers.  Integer sums
+        // do not depend on which split that is.
+        const int64_t plane_elems = (int64_t)kBM * BN;
+        const int64_t plane_stride = (int64_t)p.tiles_m * p.tiles_n * plane_elems;
+        AccT* planes = (AccT*)p.acc_scratch + (int64_t)tile * plane_elems + (int64_t)col0 * kBM + row_in_tile;
+        {
+          AccT* dst = planes + ks * plane_stride;
 #pragma unroll
-            for (int i = 0; i < kColsPerThread; ++i)
-              if (ncol0 + i < p.N) atomicAdd(dst + i, (unsigned long long)(long long)acc[i]);
-          } else {
-            int* dst = (int*)p.acc_scratch + (int64_t)row * p.N + ncol0;
-#pragma unroll
-            for (int i = 0; i < kColsPerThread; ++i)
-              if (ncol0 + i < p.N) atomicAdd(dst + i, (int)acc[i]);
-          }
+          for (int i = 0; i < kColsPerThread; ++i) __stcg(dst + i * kBM, acc[i]);
         }
         __threadfence();
-        // all 8 epilogue warps must have added before the tile counts as arrived
+        // all 8 epilogue warps must have stored before the tile counts as arrived
         if (!epi_sync()) { ok = false; break; }
         if (threadIdx.x == 64) *s_last = (atomicAdd(p.locks + tile, 1) == p.split_k - 1) ? 1 : 0;
         if (!epi_sync()) { ok = false; break; }
@@ -244,16 +242,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         if (last) {
           __threadfence();
           if (row_ok) {
-            if (p.int_bits == 64) {
-              long long* src = (long long*)p.acc_scratch + (int64_t)row * p.N + ncol0;
+            for (int s2 = 0; s2 < p.split_k; ++s2) {
+              if (s2 == ks) continue;
+              const AccT* src = planes + s2 * plane_stride;
 #pragma unroll
-              for (int i = 0; i < kColsPerThread; ++i)
-                if (ncol0 + i < p.N) { acc[i] = (AccT)__ldcg(src + i); src[i] = 0; }
-            } else {
-              int* src = (int*)p.acc_scratch + (int64_t)row * p.N + ncol0;
-#pragma unroll
-              for (int i = 0; i < kColsPerThread; ++i)
-                if (ncol0 + i < p.N) { acc[i] = (AccT)__ldcg(src + i); src[i] = 0; }
+              for (int i = 0; i < kColsPerThread; ++i) acc[i] += __ldcg(src + i * kBM);
             }
           }
           if (threadIdx.x == 64) p.locks[tile] = 0;
@@ -385,10 +378,20 @@ bool gemm_tc_supported(const GemmArgs& g) {
   return true;
 }
 
-int64_t gemm_tc_scratch_bytes(int64_t M, int64_t N, int int_bits) {
-  const int64_t acc = M * N * (int_bits == 64 ? 8 : 4);
-  const int64_t locks = ((M + kBM - 1) / kBM) * ((N + 127) / 128) * 4;
-  return ((acc + 255) / 256) * 256 + ((locks + 255) / 256) * 256;
+// Split-K scratch: [tile counters | split_k planes of integer partial tiles].  The counter
+// region has one fixed size so that a buffer reused for problems of different shapes never
+// shows plane contents as counters; only the counters must be zero before the first use,
+// and every launch leaves them zero.  Problems with more tiles than counters run unsplit
+// (they fill the GPU many times over; the result is the same bits).
+static constexpr int64_t kLockBytes = 256 * 1024;
+static constexpr int64_t kMaxSplitTiles = kLockBytes / 4;
+static int64_t tc_lock_bytes(int64_t, int64_t) { return kLockBytes; }
+
+int64_t gemm_tc_scratch_bytes(int64_t M, int64_t N, int int_bits, int split_k) {
+  const int64_t rows = ((M + kBM - 1) / kBM) * kBM;
+  const int64_t cols = ((N + 255) / 256) * 256;
+  const int64_t planes = (int64_t)(split_k < 1 ? 1 : split_k) * rows * cols * (int_bits == 64 ? 8 : 4);
+  return tc_lock_bytes(M, N) + ((planes + 255) / 256) * 256;
 }
 
 template <typename T, int BN, bool ACC64, int STAGES>
@@ -444,13 +447,13 @@ int gemm_tc(const GemmArgs& g, cudaStream_t s) {
   const int k_tiles = (int)((g.K + g.k_tile - 1) / g.k_tile);
   p.split_k = g.split_k < 1 ? 1 : (g.split_k > k_tiles ? k_tiles : g.split_k);
   p.acc_scratch = nullptr; p.locks = nullptr;
+  if (((g.M + kBM - 1) / kBM) * ((g.N + 127) / 128) > kMaxSplitTiles) p.split_k = 1;
   if (p.split_k > 1) {
-    const int64_t need = gemm_tc_scratch_bytes(g.M, g.N, g.int_bits);
+    const int64_t need = gemm_tc_scratch_bytes(g.M, g.N, g.int_bits, p.split_k);
     if (!g.scratch || g.scratch_bytes < need) return FXPR_ERR_SCRATCH;
     if ((uintptr_t)g.scratch & 15) return FXPR_ERR_BAD_ARG;
-    const int64_t acc_bytes = ((g.M * g.N * (g.int_bits == 64 ? 8 : 4) + 255) / 256) * 256;
-    p.acc_scratch = g.scratch;
-    p.locks = (int32_t*)((char*)g.scratch + acc_bytes);
+    p.locks = (int32_t*)g.scratch;
+    p.acc_scratch = (char*)g.scratch + tc_lock_bytes(g.M, g.N);
   }
 
   if (!(g.flags & FXPR_GEMM_FORCE_EXACT_TC) && gemm_tc_fast_supported(g, p.split_k)) {

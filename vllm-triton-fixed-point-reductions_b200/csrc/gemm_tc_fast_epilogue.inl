@@ -103,20 +103,23 @@
 
     const bool row_ok = row < p.M;
     bool do_store = true;
+    // Split-K: every split leaves its integer partial tile in its own plane of the scratch
+    // (column-major inside the tile, so a warp's 32 rows are 32 consecutive words and every
+    // store and load is one full line); the split that arrives last adds the planes of the
+    // others to its registers.  Integer addition is commutative and associative: which
+    // split comes last cannot change the sum.
+    const int64_t plane_elems = (int64_t)kBM * BN;
+    const int64_t plane_stride = (int64_t)p.tiles_m * p.tiles_n * plane_elems;
+    const int64_t plane_off = (int64_t)tile * plane_elems + (int64_t)col0 * kBM + row_in_tile;
     if (p.split_k > 1) {
-      // integer atomics are commutative: arrival order cannot change the sum
-      if (row_ok) {
-        if (p.int_bits == 64) {
-          unsigned long long* dst = (unsigned long long*)p.acc_scratch + (int64_t)row * p.N + ncol0;
+      if (p.int_bits == 64) {
+        long long* dst = (long long*)p.acc_scratch + ks * plane_stride + plane_off;
 #pragma unroll
-          for (int i = 0; i < kCols; ++i)
-            if (ncol0 + i < p.N) atomicAdd(dst + i, (unsigned long long)total(i));
-        } else {
-          int* dst = (int*)p.acc_scratch + (int64_t)row * p.N + ncol0;
+        for (int i = 0; i < kCols; ++i) __stcg(dst + i * kBM, total(i));
+      } else {
+        int* dst = (int*)p.acc_scratch + ks * plane_stride + plane_off;
 #pragma unroll
-          for (int i = 0; i < kCols; ++i)
-            if (ncol0 + i < p.N) atomicAdd(dst + i, (int)total(i));
-        }
+        for (int i = 0; i < kCols; ++i) __stcg(dst + i * kBM, (int)total(i));
       }
       __threadfence();
       if (!epi_sync()) { ok = false; break; }
@@ -133,22 +136,25 @@
       for (int g = 0; g < kCols / 8; ++g) {
         long long q8[8];
         const int colg = ncol0 + g * 8;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) q8[i] = total(g * 8 + i);
         if (p.split_k > 1) {
-          // read the merged sums back and leave the scratch zeroed for the next call
-          if (p.int_bits == 64) {
-            long long* src = (long long*)p.acc_scratch + (int64_t)row * p.N + colg;
+          for (int s2 = 0; s2 < p.split_k; ++s2) {
+            if (s2 == ks) continue;
+            if (p.int_bits == 64) {
+              const long long* src = (const long long*)p.acc_scratch + s2 * plane_stride + plane_off + (int64_t)g * 8 * kBM;
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
-              if (colg + i < p.N) { q8[i] = __ldcg(src + i); src[i] = 0; } else q8[i] = 0;
-          } else {
-            int* src = (int*)p.acc_scratch + (int64_t)row * p.N + colg;
+              for (int i = 0; i < 8; ++i) q8[i] += __ldcg(src + i * kBM);
+            } else {
+              const int* src = (const int*)p.acc_scratch + s2 * plane_stride + plane_off + (int64_t)g * 8 * kBM;
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
-              if (colg + i < p.N) { q8[i] = (long long)__ldcg(src + i); src[i] = 0; } else q8[i] = 0;
+              for (int i = 0; i < 8; ++i) q8[i] += (long long)__ldcg(src + i * kBM);
+            }
           }
-        } else {
+          if (p.int_bits != 64) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) q8[i] = total(g * 8 + i);
+            for (int i = 0; i < 8; ++i) q8[i] = (long long)(int32_t)q8[i];
+          }
         }
         if (p.c_int) {
           if (p.int_bits == 64) {

@@ -314,7 +314,8 @@ def pick_split_k(M: int, N: int, K: int, k_tile: int, int_bits: int, num_sms: in
     if tiles_mn >= num_sms or k_tiles < 8:
         return 1
     split = 1
-    while split < 16 and tiles_mn * split * 2 <= num_sms * 2 and k_tiles // (split * 2) >= 4:
+    # one wave of CTAs at most: a second, partly filled wave costs more than it hides
+    while split < 16 and tiles_mn * split * 2 <= num_sms and k_tiles // (split * 2) >= 4:
         split *= 2
     return split
 
