@@ -46,6 +46,7 @@ extern "C" {
 /* ---- attention flags --------------------------------------------------- */
 #define FXPR_ATTN_CAUSAL         1
 #define FXPR_ATTN_FORCE_PORTABLE 2  /* route to the CUDA-core kernel (sequential partials) */
+#define FXPR_ATTN_EXACT_CONVERT  4  /* tensor-core route with cvt.rni.sat conversions only (tests: same bits as the default) */
 
 int fxpr_version(void);
 const char* fxpr_status_string(int status);

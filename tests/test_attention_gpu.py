@@ -183,3 +183,24 @@ def test_softcap_and_errors():
         torch.ops.fxpr.unified_attention_fxp(q, kv.float(), o, qsl, sl, bt, mq, None, True, None, 32, 16, 0.0, 0, 1)
     # empty batch is a no-op
     torch.ops.fxpr.unified_attention_fxp(q[:0], kv, o[:0], qsl[:1], sl[:0], bt[:0], 0, None, True, None, 32, 16, 0.0, 0, 1)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("hq,hkv,d", [(32, 8, 128), (8, 8, 64)])
+@pytest.mark.parametrize("int_bits,frac_bits", [(64, 16), (32, 16), (64, 8)])
+@pytest.mark.parametrize("outliers", [False, True])
+def test_fast_conversion_prefill_equals_exact_conversion(dtype, hq, hkv, d, int_bits, frac_bits, outliers):
+    """The prefill kernel's second pass converts on the FP32 pipe (magic-number rounding,
+    32-bit wrap-around sums, exact fix-up for partials outside its range); the bits must be
+    those of the cvt.rni.sat kernel.  Outliers in V push P.V partials past 2^(22-frac)."""
+    from fxpr_vllm import _native as nat
+    q, kv, qsl, sl, bt, mq = _mixed_batch(dtype, hq, hkv, d, 16, 21, ctx=(300, 150, 70), qlens=(300, 5, 70))
+    if outliers:
+        kv = kv.clone()
+        kv[3::7, 1, 5, :, ::3] = 3000.0 if frac_bits == 16 else 60000.0
+        kv[2::5, 1, 9, :, 1::4] = -2500.0
+    outs = []
+    for flags in (0, nat.ATTN_EXACT_CONVERT):
+        with L.overrides(attn_flags=flags):
+            outs.append(_h().run_attention(q, kv, qsl, sl, bt, mq, int_bits=int_bits, frac_bits=frac_bits))
+    assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))

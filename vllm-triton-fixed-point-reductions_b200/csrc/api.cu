@@ -98,7 +98,7 @@ extern "C" int fxpr_attention(const void* q, const void* k_cache, const void* v_
   // The tensor-core route merges its splits through distributed shared memory and needs
   // no scratch; only the CUDA-core route uses the caller's buffer.
   if (!(flags & FXPR_ATTN_FORCE_PORTABLE) && attention_mma_supported(p, dtype))
-    return attention_mma(p, dtype, max_query_len, s);
+    return attention_mma(p, dtype, max_query_len, (flags & FXPR_ATTN_EXACT_CONVERT) != 0, s);
   if (num_splits > 1) {
     const AttnScratchLayout l = attn_scratch_layout(total_q_tokens, num_heads, head_dim, num_splits);
     if (!scratch || scratch_bytes < l.total) return FXPR_ERR_SCRATCH;

@@ -95,12 +95,17 @@ struct MmaAttnShape {
   int page_shift;          // log2(page_size) when it is a power of two, else -1
 };
 
+// Magic-number rounding of the second pass (attention_mma_pass_b_fast.inl)
+static constexpr uint32_t kAttnMagicBits = 0x4B400000u;   // 1.5 * 2^23
+static constexpr uint32_t kAttnExpBits = 0x4B000000u;     // sign 0, exponent 150: r in [2^23, 2^24)
+static constexpr int kFastMaxTiles = 500;                 // 500 * 2^22 < 2^31: the 32-bit sums cannot wrap twice
+
 #include "attention_mma_kernel.inl"
 #include "attention_mma_decode.inl"
 
 static int stash_bytes_per_key(int stash_rows) { return stash_rows <= 8 ? stash_rows * 4 : 64; }
 
-template <typename T, int HD, int NW, bool STASH, bool ACC64>
+template <typename T, int HD, int NW, bool STASH, bool ACC64, bool FAST = false>
 static int launch_mma(const AttnParams& p, const MmaAttnShape& sh, cudaStream_t s) {
   constexpr int BM = 16 * NW;
   constexpr int kTileBytes = kTileN * HD * 2;
@@ -108,7 +113,7 @@ static int launch_mma(const AttnParams& p, const MmaAttnShape& sh, cudaStream_t 
   constexpr int NSTAGE = STASH ? 3 : 2;
   size_t smem = (size_t)BM * HD * 2 + (size_t)NSTAGE * kStage + BM * 4 + BM * 8;
   if (STASH) smem += (size_t)sh.stash_keys * stash_bytes_per_key(sh.stash_rows);
-  auto k = attn_mma_kernel<T, HD, NW, STASH, ACC64>;
+  auto k = attn_mma_kernel<T, HD, NW, STASH, ACC64, FAST>;
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
   if (e != cudaSuccess) { set_last_error("attention_mma smem attribute", e); return FXPR_ERR_CUDA; }
   if (p.num_splits > 8) {
@@ -176,7 +181,7 @@ bool attention_mma_supported(const AttnParams& p, int dtype) {
   return true;
 }
 
-int attention_mma(const AttnParams& p_in, int dtype, int max_query_len, cudaStream_t s) {
+int attention_mma(const AttnParams& p_in, int dtype, int max_query_len, bool force_exact, cudaStream_t s) {
   AttnParams p = p_in;
   if (p.num_splits > 16) p.num_splits = 16;        // cluster size limit; results do not depend on it
   if (p.num_splits < 1) p.num_splits = 1;
@@ -201,6 +206,9 @@ int attention_mma(const AttnParams& p_in, int dtype, int max_query_len, cudaStre
   const bool stash = small && (int64_t)sh.stash_keys * stash_bytes_per_key(sh.stash_rows) <= 150 * 1024;
   if (!stash) sh.stash_keys = 0;
   const bool acc64 = p.int_bits == 64;
+  // fast second pass (same bits): scale <= 2^16, 32- or 64-bit sums, bounded tiles per CTA
+  const bool fast = !force_exact && p.scale <= 65536.0f && (p.int_bits == 32 || p.int_bits == 64) &&
+                    per_rank <= kFastMaxTiles;
 
 #define FXPR_ATTN(TT, HDV)                                                                      \
   do {                                                                                          \
@@ -211,6 +219,7 @@ int attention_mma(const AttnParams& p_in, int dtype, int max_query_len, cudaStre
                                      : launch_decode<TT, HDV, 4, false, false>(p, sh, s);\
     if (small) return acc64 ? launch_mma<TT, HDV, 1, false, true>(p, sh, s)                     \
                             : launch_mma<TT, HDV, 1, false, false>(p, sh, s);                   \
+    if (fast) return launch_mma<TT, HDV, 4, false, false, true>(p, sh, s);                      \
     return acc64 ? launch_mma<TT, HDV, 4, false, true>(p, sh, s)                                \
                  : launch_mma<TT, HDV, 4, false, false>(p, sh, s);                              \
   } while (0)

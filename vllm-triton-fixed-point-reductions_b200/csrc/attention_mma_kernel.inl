@@ -2,12 +2,14 @@
 //
 // Template: T = io dtype, HD = head size (64 | 128), NW = warps per CTA (16 query rows
 // each), STASH = keep this CTA's fp32 scores in shared memory between the two passes
-// (decode), ACC64 = 64-bit integer accumulators.
+// (decode), ACC64 = 64-bit integer accumulators, FAST = second pass with magic-number
+// rounding on the FP32 pipe and 32-bit wrap-around accumulators (same bits, see
+// attention_mma_pass_b_fast.inl).
 // Grid: x = KV split (= rank in the cluster), y = q_block * num_kv_heads + kv_head,
 // z = request.
 
-template <typename T, int HD, int NW, bool STASH, bool ACC64>
-__global__ void __launch_bounds__(NW * 32)
+template <typename T, int HD, int NW, bool STASH, bool ACC64, bool FAST>
+__global__ void __launch_bounds__(NW * 32, FAST ? 3 : 1)
 attn_mma_kernel(const AttnParams p, const MmaAttnShape sh) {
   constexpr int RC = HD / 8;                       // 16-byte chunks per K/V/Q row
   constexpr int BM = 16 * NW;                      // query rows per CTA
@@ -83,29 +85,35 @@ attn_mma_kernel(const AttnParams p, const MmaAttnShape sh) {
 
   const T* kbase = (const T*)p.k + (int64_t)kvh * p.kv_shead;
   const T* vbase = (const T*)p.v + (int64_t)kvh * p.kv_shead;
-  const int pages_per_tile = kTileN / 16;          // block-table entries are looked up per 16 keys
 
-  // stage one 64-key tile of K or V: 16-byte cp.async per (key, chunk); rows past the
-  // sequence are zero-filled and never touch the block table
-  auto issue_tile = [&](const T* base, int t, uint32_t dst) {
-    int64_t page_off[4];
-#pragma unroll
-    for (int q4 = 0; q4 < pages_per_tile; ++q4) {
+  // stage one 64-key tile of K and/or V: 16-byte cp.async per (key, chunk); rows past the
+  // sequence are zero-filled and never touch the block table.  The block table is looked
+  // up once per 16 keys and the four page offsets stay in scalars (a dynamically indexed
+  // array would live in local memory).
+  auto issue_kv = [&](int t, uint32_t dst_k, uint32_t dst_v, bool want_k, bool want_v) {
+    auto page_of = [&](int q4) -> int64_t {
       const int n = t * kTileN + q4 * 16;
-      page_off[q4] = (n < seq_len) ? (int64_t)bt[n / p.page_size] * p.kv_sblock +
-                                         (int64_t)(n % p.page_size) * p.kv_sslot
-                                   : -1;
-    }
+      return (n < seq_len) ? (int64_t)bt[n / p.page_size] * p.kv_sblock +
+                                 (int64_t)(n % p.page_size) * p.kv_sslot
+                           : 0;
+    };
+    const int64_t po0 = page_of(0), po1 = page_of(1), po2 = page_of(2), po3 = page_of(3);
 #pragma unroll
     for (int it = 0; it < kTileN * RC / NT; ++it) {
       const int idx = threadIdx.x + it * NT;
       const int key = idx / RC, c = idx % RC;
-      const int n = t * kTileN + key;
-      const bool v = n < seq_len;
-      const int64_t po = page_off[key >> 4];
-      const T* src = v ? base + po + (int64_t)(key & 15) * p.kv_sslot + c * 8 : base;
-      cp_async16(dst + swz<RC>(key, c), src, v);
+      const bool v = t * kTileN + key < seq_len;
+      const int q4 = key >> 4;
+      const int64_t po = q4 == 0 ? po0 : (q4 == 1 ? po1 : (q4 == 2 ? po2 : po3));
+      const int64_t off = v ? po + (int64_t)(key & 15) * p.kv_sslot + c * 8 : 0;
+      const uint32_t so = swz<RC>(key, c);
+      if (want_k) cp_async16(dst_k + so, kbase + off, v);
+      if (want_v) cp_async16(dst_v + so, vbase + off, v);
     }
+  };
+  auto issue_tile = [&](const T* base, int t, uint32_t dst) {
+    if (base == kbase) issue_kv(t, dst, 0, true, false);
+    else issue_kv(t, 0, dst, false, true);
   };
 
   const uint32_t stage0 = smem_addr(stage_s);

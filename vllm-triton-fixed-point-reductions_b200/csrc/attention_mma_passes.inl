@@ -54,6 +54,9 @@
     gmax[h] = (m == ninf) ? 0.0f : m;               // rows without keys: exp2 gives 0, not NaN
   }
 
+  if constexpr (FAST) {
+#include "attention_mma_pass_b_fast.inl"
+  } else {
   // =============================== pass B =============================================
   long long den[2] = {0, 0};
   AccT acc[HD / 8][4];
@@ -63,8 +66,8 @@
     // STASH: a stage holds one V tile.  Otherwise a stage holds K then V.
     auto issue_b = [&](int t) {
       const uint32_t dst = stage0 + (t - t0) % NSTAGE * kStageBytes;
-      if (!STASH) issue_tile(kbase, t, dst);
-      issue_tile(vbase, t, STASH ? dst : dst + kTileBytes);
+      if (STASH) issue_kv(t, 0, dst, false, true);
+      else issue_kv(t, dst, dst + kTileBytes, true, true);
     };
     __syncthreads();                                 // everyone is done with pass A's stages
     int issued = t0;
@@ -151,6 +154,7 @@
       wv_s[(size_t)r * HD + j * 8 + 2 * t4] = (long long)acc[j][2 * h];
       wv_s[(size_t)r * HD + j * 8 + 2 * t4 + 1] = (long long)acc[j][2 * h + 1];
     }
+  }
   }
   cluster.sync();
   if (rank == 0) {

@@ -95,6 +95,7 @@ class _Overrides(threading.local):
     attn_portable: bool = False
     gemm_partials: bool = False
     gemm_flags: int = 0
+    attn_flags: int = 0
     last_partials: torch.Tensor | None = None
 
 
@@ -103,11 +104,12 @@ _ovr = _Overrides()
 
 @contextlib.contextmanager
 def overrides(*, gemm_k_tile=None, gemm_split_k=None, gemm_portable=None,
-              attn_portable=None, gemm_partials=None, gemm_flags=None):
+              attn_portable=None, gemm_partials=None, gemm_flags=None, attn_flags=None):
     """Temporarily pin kernel-selection knobs (K-tile, split-K, portable route)."""
     names = ("gemm_k_tile", "gemm_split_k", "gemm_portable", "attn_portable", "gemm_partials",
-             "gemm_flags")
-    vals = (gemm_k_tile, gemm_split_k, gemm_portable, attn_portable, gemm_partials, gemm_flags)
+             "gemm_flags", "attn_flags")
+    vals = (gemm_k_tile, gemm_split_k, gemm_portable, attn_portable, gemm_partials, gemm_flags,
+            attn_flags)
     old = {n: getattr(_ovr, n) for n in names}
     try:
         for n, v in zip(names, vals):
@@ -503,7 +505,8 @@ def unified_attention_fxp_run(q, kv_cache, o, query_start_loc, seq_lens, block_t
                                                          fxp_int_bits, splits)
         scratch = torch.empty(scratch_bytes, device=q.device, dtype=torch.uint8)
     alibi = alibi_slopes.contiguous() if has_alibi else None
-    flags = (nat.ATTN_CAUSAL if is_causal else 0) | (nat.ATTN_FORCE_PORTABLE if _ovr.attn_portable else 0)
+    flags = ((nat.ATTN_CAUSAL if is_causal else 0) | (nat.ATTN_FORCE_PORTABLE if _ovr.attn_portable else 0)
+             | int(_ovr.attn_flags))
     k_cache = kv_cache.select(1, 0)
     v_cache = kv_cache.select(1, 1)
     qsl = query_start_loc.contiguous()
