@@ -266,12 +266,93 @@ def run_gpu_arm(args):
     }
     if not args.skip_others:
         line["others"] = bench_others(dev, peaks, L, syn)
+    if not args.skip_model:
+        line.setdefault("others", {})["llama3_8b_decode_cfg4"] = bench_llama(dev, dist, world, peaks)
     if rank == 0:
         if not args.skip_cpu:
             line["cpu_baseline"] = cpu_gemm_baseline(256)
         print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()
+
+
+def _digest(t: torch.Tensor) -> int:
+    """Position-sensitive 64-bit checksum of a 16-bit tensor's bit patterns."""
+    v = t.contiguous().view(torch.int16).reshape(-1).to(torch.int64)
+    w = torch.arange(v.numel(), device=v.device, dtype=torch.int64) % 65521 + 1
+    return int((v * w).sum().item())
+
+
+def bench_llama(dev, dist, world, peaks, batch=64, prompt_len=1024, gen=256):
+    """cfg4: random-init Llama-3-8B-shaped decoder, 64 sequences x 1024 prompt tokens, 256
+    greedy decode steps, tensor parallel over all ranks of the job (TP = n_gpus) with the
+    integer all-reduce.  The logits digests must be the same for every TP degree."""
+    from fxpr_vllm.llama_decoder import DecoderConfig, DistGroup, LlamaDecoder, LocalGroup
+
+    cfg = DecoderConfig()
+    group = DistGroup() if dist is not None else LocalGroup(1)
+    t0 = time.time()
+    model = LlamaDecoder(cfg, group, dev, seed=0, max_seqs=batch, max_len=prompt_len + gen)
+    g = torch.Generator().manual_seed(7)
+    prompts = torch.randint(0, cfg.vocab, (batch, prompt_len), generator=g).to(dev)
+    torch.cuda.synchronize()
+    build_s = time.time() - t0
+
+    def timed(fn):
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        out = fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if dist is not None:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return out, float(ms.item())
+
+    logits, prefill_ms = timed(lambda: model.prefill(prompts))
+    d_prefill = _digest(logits)
+    state = {"tok": model.greedy(logits), "logits": logits}
+
+    def decode_all():
+        for step in range(gen):
+            state["logits"] = model.decode_step(state["tok"], prompt_len + step)
+            state["tok"] = model.greedy(state["logits"])
+
+    graph_error = None
+    try:
+        model.capture_decode(state["tok"], prompt_len)
+
+        def decode_all_graph():
+            for _ in range(gen):
+                state["logits"] = model.replay_decode()
+
+        _, decode_ms = timed(decode_all_graph)
+        state["tok"] = model._g_tok
+        launch = "one CUDA graph per decode step"
+    except Exception as e:  # capture not possible (for example an old NCCL): time the eager loop
+        graph_error = repr(e)[:200]
+        _, decode_ms = timed(decode_all)
+        launch = "python-launched ops"
+    weights_gb = (cfg.layers * (cfg.hidden * (cfg.q_heads + 2 * cfg.kv_heads) * cfg.head_dim
+                                + cfg.q_heads * cfg.head_dim * cfg.hidden + 3 * cfg.hidden * cfg.ffn)
+                  + cfg.hidden * cfg.vocab) * 2 / 1e9
+    kv_gb = batch * (prompt_len + gen / 2) * cfg.layers * 2 * cfg.kv_heads * cfg.head_dim * 2 / 1e9
+    step_ms = decode_ms / gen
+    return {
+        "tp": world, "decode_tokens_per_s": batch * gen / (decode_ms / 1e3), "decode_ms_per_step": step_ms,
+        "prefill_ms": prefill_ms, "prefill_tokens_per_s": batch * prompt_len / (prefill_ms / 1e3),
+        "algorithmic_GB_per_step": weights_gb + kv_gb,
+        "frac_hbm_measured": (weights_gb + kv_gb) / world / (step_ms / 1e3) / peaks["hbm_gbs"],
+        "logits_digest_prefill": d_prefill, "logits_digest_last": _digest(state["logits"]),
+        "last_tokens_digest": int((state["tok"] * (torch.arange(batch, device=dev) + 1)).sum().item()),
+        "build_s": build_s,
+        "launch": launch, "graph_error": graph_error,
+        "note": "digests are equal across TP degrees when the integer all-reduce keeps the logits "
+                "bit-identical",
+    }
 
 
 def bench_others(dev, peaks, L, syn):
@@ -351,6 +432,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-others", action="store_true")
     ap.add_argument("--skip-cpu", action="store_true")
+    ap.add_argument("--skip-model", action="store_true", help="skip the cfg4 decoder run")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

@@ -1,0 +1,277 @@
+"""Random-init Llama-shaped decoder wired through the fixed-point ops, with tensor
+parallelism whose only exchange is an integer all-reduce.
+
+This is the workload of the fifth benchmark configuration (Llama-3-8B geometry, 64 decode
+sequences, greedy sampling, TP = 1/2/4/8 with bit-identical logits), not a model zoo: no
+checkpoint, no tokenizer, weights ~ N(0, 0.02) from a seeded generator.  Every reduction
+runs in the integer domain: the GEMMs (``gemm_fxp`` / ``gemm_fxp_int``), the attention
+(``unified_attention_fxp``), the norms (``rms_norm_fxp*``); RoPE, SiLU*mul and the KV-cache
+write are element-wise torch ops.
+
+Sharding follows vLLM's Llama (``vllm/model_executor/models/llama.py``): QKV and gate/up
+column-parallel, attention heads split, o_proj and down_proj row-parallel, lm_head
+vocab-parallel (all-gather), embedding and norms replicated.  A row-parallel layer keeps its
+K-shard's integer accumulators, the group sums them (associative: any reduction order gives
+the same bits), then one fixed->float epilogue runs on every rank.
+
+``LocalGroup`` holds all shards in one process (single-GPU emulation used by the tests);
+``DistGroup`` holds one shard per process and reduces with ``torch.distributed``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+from . import library_ops as ops
+from ._lib import BLOCK_K_BY_DTYPE
+from .config import get_runtime_config
+from .tp import check_shardable
+
+
+@dataclass
+class DecoderConfig:
+    hidden: int = 4096
+    ffn: int = 14336
+    q_heads: int = 32
+    kv_heads: int = 8
+    head_dim: int = 128
+    vocab: int = 128256
+    layers: int = 32
+    dtype: torch.dtype = torch.bfloat16
+    page: int = 16
+    rope_theta: float = 500000.0
+    eps: float = 1e-5
+    int_bits: int = 64
+    frac_bits: int = 16
+    init_std: float = 0.02
+
+
+class LocalGroup:
+    """All ``size`` tensor-parallel shards live in this process (one GPU)."""
+
+    def __init__(self, size: int):
+        self.size = size
+        self.local_ranks = list(range(size))
+
+    def all_reduce_int(self, parts):
+        total = parts[0].clone()
+        for t in parts[1:]:
+            total += t
+        return [total] * len(parts)
+
+    def all_gather_cols(self, parts):
+        return torch.cat(parts, dim=-1)
+
+
+class DistGroup:
+    """One shard per process; ``torch.distributed`` carries the integer sums."""
+
+    def __init__(self, group=None):
+        self.group = group
+        self.size = dist.get_world_size(group)
+        self.local_ranks = [dist.get_rank(group)]
+
+    def all_reduce_int(self, parts):
+        if self.size > 1:
+            dist.all_reduce(parts[0], op=dist.ReduceOp.SUM, group=self.group)
+        return parts
+
+    def all_gather_cols(self, parts):
+        if self.size == 1:
+            return parts[0]
+        out = [torch.empty_like(parts[0]) for _ in range(self.size)]
+        dist.all_gather(out, parts[0].contiguous(), group=self.group)
+        return torch.cat(out, dim=-1)
+
+
+def _full_weight(shape, seed, device, dtype, std):
+    g = torch.Generator(device=device).manual_seed(seed)
+    return (std * torch.randn(shape, generator=g, device=device, dtype=torch.float32)).to(dtype)
+
+
+class _Shard:
+    """The weights and KV cache of one tensor-parallel rank."""
+
+    def __init__(self):
+        self.qkv = []
+        self.o = []
+        self.gate_up = []
+        self.down = []
+        self.lm_head = None
+        self.kv_cache = []
+
+
+class LlamaDecoder:
+    def __init__(self, cfg: DecoderConfig, group, device, *, seed: int = 0, max_seqs: int = 64,
+                 max_len: int = 1280):
+        self.cfg, self.group, self.device = cfg, group, torch.device(device)
+        tp = group.size
+        if cfg.q_heads % tp or cfg.kv_heads % tp or cfg.ffn % tp or cfg.vocab % tp:
+            raise ValueError(f"tp={tp} does not divide the head / ffn / vocab sizes")
+        k_tile = get_runtime_config().gemm_k_tile or BLOCK_K_BY_DTYPE[cfg.dtype]
+        check_shardable(cfg.q_heads * cfg.head_dim, tp, k_tile)
+        check_shardable(cfg.ffn, tp, k_tile)
+        self.qh, self.kvh = cfg.q_heads // tp, cfg.kv_heads // tp
+        hd, H = cfg.head_dim, cfg.hidden
+        self.blocks_per_seq = -(-max_len // cfg.page)
+        self.max_seqs = max_seqs
+        self.shards = {r: _Shard() for r in group.local_ranks}
+        dev, dt, std = self.device, cfg.dtype, cfg.init_std
+
+        self.embed = _full_weight((cfg.vocab, H), seed * 1000 + 1, dev, dt, 1.0)
+        self.norm_w = [torch.ones(H, device=dev, dtype=dt) for _ in range(2 * cfg.layers + 1)]
+        for layer in range(cfg.layers):
+            s0 = seed * 1000 + 10 * (layer + 1)
+            # (K, N) row-major, the layout FixedPointLinearMethod keeps (quantisation_config.py)
+            wq = _full_weight((H, cfg.q_heads * hd), s0 + 1, dev, dt, std)
+            wk = _full_weight((H, cfg.kv_heads * hd), s0 + 2, dev, dt, std)
+            wv = _full_weight((H, cfg.kv_heads * hd), s0 + 3, dev, dt, std)
+            wo = _full_weight((cfg.q_heads * hd, H), s0 + 4, dev, dt, std)
+            wg = _full_weight((H, cfg.ffn), s0 + 5, dev, dt, std)
+            wu = _full_weight((H, cfg.ffn), s0 + 6, dev, dt, std)
+            wd = _full_weight((cfg.ffn, H), s0 + 7, dev, dt, std)
+            for r, sh in self.shards.items():
+                q0, k0, f0 = r * self.qh * hd, r * self.kvh * hd, r * (cfg.ffn // tp)
+                sh.qkv.append(torch.cat([wq[:, q0:q0 + self.qh * hd], wk[:, k0:k0 + self.kvh * hd],
+                                         wv[:, k0:k0 + self.kvh * hd]], dim=1).contiguous())
+                sh.o.append(wo[q0:q0 + self.qh * hd].contiguous())
+                sh.gate_up.append(torch.cat([wg[:, f0:f0 + cfg.ffn // tp],
+                                             wu[:, f0:f0 + cfg.ffn // tp]], dim=1).contiguous())
+                sh.down.append(wd[f0:f0 + cfg.ffn // tp].contiguous())
+                sh.kv_cache.append(torch.zeros((max_seqs * self.blocks_per_seq + 1, 2, cfg.page,
+                                                self.kvh, hd), device=dev, dtype=dt))
+            del wq, wk, wv, wo, wg, wu, wd
+        wl = _full_weight((H, cfg.vocab), seed * 1000 + 2, dev, dt, std)
+        vs = cfg.vocab // tp
+        for r, sh in self.shards.items():
+            sh.lm_head = wl[:, r * vs:(r + 1) * vs].contiguous()
+        del wl
+        # block 0 is left unused so that a zero block-table entry never aliases live data
+        self.block_table = (torch.arange(max_seqs * self.blocks_per_seq, device=dev, dtype=torch.int32)
+                            .reshape(max_seqs, self.blocks_per_seq) + 1)
+        inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, hd, 2, device=dev, dtype=torch.float32) / hd))
+        ang = torch.arange(max_len, device=dev, dtype=torch.float32)[:, None] * inv[None, :]
+        self.cos, self.sin = ang.cos(), ang.sin()
+
+    # ------------------------------------------------------------------ pieces
+    def _rope(self, x: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
+        """Rotate-half RoPE in fp32 (element-wise, no reduction)."""
+        half = self.cfg.head_dim // 2
+        cos, sin = self.cos[pos][:, None, :], self.sin[pos][:, None, :]
+        x1, x2 = x[..., :half].float(), x[..., half:].float()
+        return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1).to(x.dtype)
+
+    def _write_kv(self, cache, k, v, seq_ids, pos):
+        blk = self.block_table[seq_ids, pos // self.cfg.page].long()
+        slot = pos % self.cfg.page
+        cache[blk, 0, slot] = k
+        cache[blk, 1, slot] = v
+
+    def _row_parallel(self, acts, weights):
+        c = self.cfg
+        accs = [ops.gemm_fxp_int(a, w, c.int_bits, c.frac_bits) for a, w in zip(acts, weights)]
+        accs = self.group.all_reduce_int(accs)
+        return ops.gemm_fxp_epilogue(accs[0], None, c.dtype, c.frac_bits)
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, tokens, seq_ids, pos, qsl, seq_lens, max_q: int) -> torch.Tensor:
+        """tokens/seq_ids/pos: [T] (flattened batch); returns the logits of each sequence's
+        last token, [B, vocab] in the io dtype, identical on every rank."""
+        c = self.cfg
+        T, hd = tokens.numel(), c.head_dim
+        shards = [self.shards[r] for r in self.group.local_ranks]
+        bt = self.block_table[: seq_lens.numel()]
+        x = self.embed[tokens]
+        residual = None
+        for layer in range(c.layers):
+            if residual is None:
+                residual = x.clone()
+                h = ops.rms_norm_fxp(x, self.norm_w[2 * layer], c.eps)
+            else:
+                h = ops.rms_norm_fxp_residual(x, residual, self.norm_w[2 * layer], c.eps)
+            outs = []
+            for sh in shards:
+                qkv = ops.gemm_fxp(h, sh.qkv[layer], None, c.int_bits, c.frac_bits)
+                q, k, v = qkv.split([self.qh * hd, self.kvh * hd, self.kvh * hd], dim=1)
+                q = self._rope(q.reshape(T, self.qh, hd), pos)
+                k = self._rope(k.reshape(T, self.kvh, hd), pos)
+                self._write_kv(sh.kv_cache[layer], k, v.reshape(T, self.kvh, hd), seq_ids, pos)
+                o = torch.empty_like(q)
+                ops.unified_attention_fxp(q, sh.kv_cache[layer], o, qsl, seq_lens, bt, max_q, None, True,
+                                          None, c.int_bits, c.frac_bits, 0.0, 0, 0)
+                outs.append(o.reshape(T, self.qh * hd))
+            x = self._row_parallel(outs, [sh.o[layer] for sh in shards])
+            h = ops.rms_norm_fxp_residual(x, residual, self.norm_w[2 * layer + 1], c.eps)
+            acts = []
+            for sh in shards:
+                gu = ops.gemm_fxp(h, sh.gate_up[layer], None, c.int_bits, c.frac_bits)
+                f = gu.shape[1] // 2
+                acts.append((torch.nn.functional.silu(gu[:, :f].float()) * gu[:, f:].float()).to(c.dtype))
+            x = self._row_parallel(acts, [sh.down[layer] for sh in shards])
+        h = ops.rms_norm_fxp_residual(x, residual, self.norm_w[2 * c.layers], c.eps)
+        last = h[(qsl[1:] - 1).long()]
+        parts = [ops.gemm_fxp(last, sh.lm_head, None, c.int_bits, c.frac_bits) for sh in shards]
+        return self.group.all_gather_cols(parts)
+
+    # ------------------------------------------------------------------ generation
+    def prefill(self, prompts: torch.Tensor) -> torch.Tensor:
+        """prompts [B, L] int64 -> logits [B, vocab] of the last prompt token."""
+        B, L = prompts.shape
+        dev = self.device
+        seq_ids = torch.arange(B, device=dev).repeat_interleave(L)
+        pos = torch.arange(L, device=dev).repeat(B)
+        qsl = torch.arange(B + 1, device=dev, dtype=torch.int32) * L
+        seq_lens = torch.full((B,), L, device=dev, dtype=torch.int32)
+        return self.forward(prompts.reshape(-1), seq_ids, pos, qsl, seq_lens, L)
+
+    def decode_step(self, tokens: torch.Tensor, cur_len: int) -> torch.Tensor:
+        """tokens [B] are appended at position ``cur_len`` of every sequence."""
+        B = tokens.numel()
+        dev = self.device
+        seq_ids = torch.arange(B, device=dev)
+        pos = torch.full((B,), cur_len, device=dev, dtype=torch.long)
+        qsl = torch.arange(B + 1, device=dev, dtype=torch.int32)
+        seq_lens = torch.full((B,), cur_len + 1, device=dev, dtype=torch.int32)
+        return self.forward(tokens, seq_ids, pos, qsl, seq_lens, 1)
+
+    @staticmethod
+    def greedy(logits: torch.Tensor) -> torch.Tensor:
+        return logits.float().argmax(dim=-1)
+
+    # ------------------------------------------------------------------ CUDA-graph decode
+    def capture_decode(self, first_tokens: torch.Tensor, start_len: int):
+        """Capture one greedy decode step (forward + argmax + position update) in a CUDA
+        graph; ``replay_decode()`` then runs a step with a single launch.  Positions, lengths
+        and the current tokens live in device tensors that the graph itself advances."""
+        B, dev = first_tokens.numel(), self.device
+        self._g_tok = first_tokens.clone()
+        self._g_pos = torch.full((B,), start_len, device=dev, dtype=torch.long)
+        self._g_lens = torch.full((B,), start_len + 1, device=dev, dtype=torch.int32)
+        self._g_ids = torch.arange(B, device=dev)
+        self._g_qsl = torch.arange(B + 1, device=dev, dtype=torch.int32)
+
+        def step():
+            logits = self.forward(self._g_tok, self._g_ids, self._g_pos, self._g_qsl, self._g_lens, 1)
+            return logits
+
+        # eager warm-up on a side stream (allocations, split-K scratch, module state); it
+        # writes the KV slot at start_len, which the first replay overwrites with the same data
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            step()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        self._graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self._graph):
+            self._g_logits = step()
+            self._g_tok.copy_(self.greedy(self._g_logits))
+            self._g_pos += 1
+            self._g_lens += 1
+
+    def replay_decode(self) -> torch.Tensor:
+        """One captured decode step; returns the logits buffer (overwritten by the next replay)."""
+        self._graph.replay()
+        return self._g_logits
