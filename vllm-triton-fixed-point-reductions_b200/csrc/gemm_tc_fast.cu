@@ -33,6 +33,8 @@
 
 namespace fxpr {
 
+__device__ __forceinline__ int lane_id() { return threadIdx.x & 31; }
+
 static constexpr uint32_t kMagicBits = 0x4B400000u;      // 1.5 * 2^23
 static constexpr uint32_t kExpBits = 0x4B000000u;        // exponent pattern of [2^23, 2^24)
 
@@ -74,7 +76,7 @@ static constexpr int kSSBytesA = 2 * kBM * kBK * 2;      // two 64-deep halves o
 // A "super-stage" is 128 deep in K: for k_tile = 128 it is one K-tile (one TMEM buffer),
 // for k_tile = 64 it is a PAIR of K-tiles whose accumulators go to the two buffers of a
 // TMEM group.  One full/empty hand-off and one tfull/tempty hand-off per super-stage.
-template <typename T, int BN, int EPIW, bool DUMP>
+template <typename T, int BN, int EPIW, bool DUMP, bool TRACE>
 __global__ void __launch_bounds__((kRoleWarps + EPIW) * 32, 1)
 gemm_tc_fast_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                     const TcParams p, const int zero /* always 0: keeps the side arrays in local memory */) {
@@ -115,6 +117,14 @@ gemm_tc_fast_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // TRACE (timing study only): CTA 0 records clock64 stamps of its first 64 super-stages
+  // into the buffer passed as `partials`: [role][super-stage][slot], 4 slots each.
+  auto trace = [&](int role, int idx, int slot) {
+    if constexpr (TRACE) {
+      if (blockIdx.x == 0 && lane_id() == 0 && idx < 64)
+        reinterpret_cast<long long*>(p.partials)[(role * 64 + idx) * 4 + slot] = clock64();
+    }
+  };
 
   const int tiles_mn = p.tiles_m * p.tiles_n;
   const int items = tiles_mn * p.split_k;
@@ -137,6 +147,7 @@ gemm_tc_fast_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     {
       const bool bk = p.b_kmajor != 0;
       int stage = 0; uint32_t phase = 1;               // "empty" waits start one phase ahead
+      int gss = 0;
       for (int item = blockIdx.x; item < items; item += gridDim.x) {
         int pm, pn; tile_coords(item / p.split_k, pm, pn);
         const int m0 = pm * kBM, n0 = pn * BN;
@@ -150,6 +161,7 @@ gemm_tc_fast_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           const int kb = pairs ? ka + p.split_k * 64 : ka + 64;
           const bool two = pairs ? (2 * ss + 1 < n_kt) : true;
           if (!__all_sync(0xffffffffu, mbar_wait(empty0 + 8u * stage, phase, abort_flag))) goto producer_done;
+          trace(0, gss, 0);
           const uint32_t fb = full0 + 8u * stage;
           const uint32_t sa = smem_base + stage * kSSBytes;
           const uint32_t sb = sa + kSSBytesA;
@@ -167,6 +179,8 @@ gemm_tc_fast_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             }
           }
           __syncwarp();
+          trace(0, gss, 1);
+          ++gss;
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -188,6 +202,7 @@ gemm_tc_fast_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       constexpr uint64_t kHalfA = (kSSBytesA / 2) >> 4, kHalfB = (kSSBytesB / 2) >> 4;
       const uint32_t idesc = p.idesc;
       int stage = 0; uint32_t phase = 0; int grp = 0; uint32_t gphase = 1;
+      int gss = 0;
       for (int item = blockIdx.x; item < items; item += gridDim.x) {
         const int ks = item % p.split_k;
         const int n_kt = (k_tiles_total - ks + p.split_k - 1) / p.split_k;
@@ -196,7 +211,9 @@ gemm_tc_fast_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           const bool two = pairs ? (2 * ss + 1 < n_kt) : true;
           {
             const bool r1 = mbar_wait(tempty0 + 8u * grp, gphase, abort_flag);
+            trace(1, gss, 0);
             const bool r2 = mbar_wait(full0 + 8u * stage, phase, abort_flag);
+            trace(1, gss, 1);
             if (!__all_sync(0xffffffffu, r1 && r2)) goto issuer_done;
           }
           tc_fence_after();
@@ -219,6 +236,8 @@ gemm_tc_fast_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           umma_commit(tfull0 + 8u * grp);              // accumulator(s) of this super-stage complete
           }
           __syncwarp();
+          trace(1, gss, 2);
+          ++gss;
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
           grp ^= 1; if (grp == 0) gphase ^= 1;
         }
@@ -245,10 +264,10 @@ gemm_tc_fast_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   }
 }
 
-template <typename T, int BN, int EPIW, bool DUMP>
+template <typename T, int BN, int EPIW, bool DUMP, bool TRACE = false>
 static int launch_fast(const CUtensorMap& ma, const CUtensorMap& mb, TcParams& p, int sms, cudaStream_t s) {
   constexpr int kSmem = 3 * (kSSBytesA + 2 * BN * kBK * 2) + 256 + 1024;
-  auto k = gemm_tc_fast_kernel<T, BN, EPIW, DUMP>;
+  auto k = gemm_tc_fast_kernel<T, BN, EPIW, DUMP, TRACE>;
   static bool attr_done = false;
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
@@ -281,13 +300,13 @@ int gemm_tc_fast(const GemmArgs& g, TcParams& p, const CUtensorMap& ma, const CU
   if (sms < 0) return FXPR_ERR_ARCH;
   (void)bn;
   p.idesc = make_idesc(g.dtype == FXPR_BF16 ? 1 : 0, p.b_kmajor ? 0 : 1, 128, kBM);
-  const bool dump = p.partials != nullptr;
-  const bool w8 = (g.flags & 16) != 0;     // experiment switch: 8 epilogue warps
+  const bool trace = (g.flags & 32) != 0 && p.partials != nullptr;   // timing study, see the kernel
+  const bool dump = p.partials != nullptr && !trace;
 #define FXPR_FAST(TT)                                                                              \
   do {                                                                                             \
     if (dump) return launch_fast<TT, 128, 16, true>(ma, mb, p, sms, s);                            \
-    return w8 ? launch_fast<TT, 128, 8, false>(ma, mb, p, sms, s)                                  \
-              : launch_fast<TT, 128, 16, false>(ma, mb, p, sms, s);                                \
+    if (trace) return launch_fast<TT, 128, 16, false, true>(ma, mb, p, sms, s);                    \
+    return launch_fast<TT, 128, 16, false>(ma, mb, p, sms, s);                                     \
   } while (0)
   if (g.dtype == FXPR_BF16) FXPR_FAST(__nv_bfloat16);
   FXPR_FAST(__half);

@@ -10,6 +10,8 @@
   const float magic = __uint_as_float(kMagicBits);
   const float scale = p.scale;
   int grp = 0; uint32_t gphase = 0; uint32_t epi_phase = 0; bool ok = true;
+  int gss = 0;
+  const int trole = warp == 2 ? 2 : (warp == 5 ? 3 : -1);
   auto epi_sync = [&]() -> bool {   // bounded barrier over the epilogue warps only
     __syncwarp();
     if (lane == 0) mbar_arrive(epi_bar);
@@ -39,48 +41,70 @@
     const int n_ss = pairs ? (n_kt + 1) >> 1 : n_kt;
     for (int ss = 0; ss < n_ss; ++ss) {
       if (!warp_wait(tfull0 + 8u * grp, gphase, abort_flag, lane)) { ok = false; break; }
+      if (trole >= 0) trace(trole, gss, 0);
       tc_fence_after();
       const int nbuf = (pairs && 2 * ss + 1 < n_kt) ? 2 : 1;
-      for (int h = 0; h < nbuf; ++h) {
-        const uint32_t taddr = tmem_base + lane_addr + (uint32_t)((grp * 2 + h) * BN);
-        // Hot loop: r = fma(p, 2^f, MAGIC) on the FP32 pipe, raw bit patterns added as
-        // integers, and the OR of the raw fp32 bits as a screen: bit 30 stays clear only
-        // if every |p| < 2, which (f <= 21) implies |p * 2^f| < 2^22.
-        uint32_t screen = 0;
+      // Hot path: r = fma(p, 2^f, MAGIC) on the FP32 pipe, raw bit patterns added as
+      // integers, and the OR of the raw fp32 bits as a screen: bit 30 stays clear only if
+      // every |p| < 2, which (f <= 21) implies |p * 2^f| < 2^22.
+      // The TMEM loads are software-pipelined: the load of the next 16 columns is in
+      // flight while the current 16 are converted, so its latency (the four warps of a
+      // scheduler are released together and would otherwise all sit in wait::ld at the
+      // same time) overlaps the arithmetic.
+      static_assert(kCols == 32, "two 16-column chunks per accumulator buffer");
+      const uint32_t ta0 = tmem_base + lane_addr + (uint32_t)((grp * 2) * BN);
+      const uint32_t ta1 = ta0 + BN;
+      uint32_t va[16], vb[16];
+      uint32_t screen0 = 0, screen1 = 0;
+      auto convert = [&](const uint32_t (&v)[16], int c, uint32_t& screen, int h) {
 #pragma unroll
-        for (int c = 0; c < kCols / 16; ++c) {
-          uint32_t v[16];
-          tmem_ld16(taddr + c * 16, v);
-          tmem_wait_ld();
+        for (int i = 0; i < 16; i += 2) {
+          acc[c * 16 + i] += __float_as_uint(__fmaf_rn(__uint_as_float(v[i]), scale, magic));
+          acc[c * 16 + i + 1] += __float_as_uint(__fmaf_rn(__uint_as_float(v[i + 1]), scale, magic));
+          screen |= v[i] | v[i + 1];
+        }
+        if (DUMP) {
+          if (row < p.M) {
+            const int kt = pairs ? ks + (2 * ss + h) * p.split_k : ks + ss * p.split_k;
+            float* dst = p.partials + ((int64_t)kt * p.M + row) * p.N + ncol0 + c * 16;
 #pragma unroll
-          for (int i = 0; i < 16; i += 2) {
-            acc[c * 16 + i] += __float_as_uint(__fmaf_rn(__uint_as_float(v[i]), scale, magic));
-            acc[c * 16 + i + 1] += __float_as_uint(__fmaf_rn(__uint_as_float(v[i + 1]), scale, magic));
-            screen |= v[i] | v[i + 1];
-          }
-          if (DUMP) {
-            if (row < p.M) {
-              const int kt = pairs ? ks + (2 * ss + h) * p.split_k : ks + ss * p.split_k;
-              float* dst = p.partials + ((int64_t)kt * p.M + row) * p.N + ncol0 + c * 16;
-#pragma unroll
-              for (int i = 0; i < 16; ++i)
-                if (ncol0 + c * 16 + i < p.N) dst[i] = __uint_as_float(v[i]);
-            }
+            for (int i = 0; i < 16; ++i)
+              if (ncol0 + c * 16 + i < p.N) dst[i] = __uint_as_float(v[i]);
           }
         }
-        if (__any_sync(0xffffffffu, (screen & 0x40000000u) != 0)) {
-          // exact fix-up for this K-tile (rare): see fixup_tile
-          if (!corr_used) {
+      };
+      tmem_ld16(ta0, va);
+      tmem_wait_ld_regs(va);
+      tmem_ld16(ta0 + 16, vb);
+      convert(va, 0, screen0, 0);
+      tmem_wait_ld_regs(vb);
+      if (nbuf == 2) tmem_ld16(ta1, va);
+      convert(vb, 1, screen0, 0);
+      if (nbuf == 2) {
+        tmem_wait_ld_regs(va);
+        tmem_ld16(ta1 + 16, vb);
+        convert(va, 0, screen1, 1);
+        tmem_wait_ld_regs(vb);
+        convert(vb, 1, screen1, 1);
+      }
+      if (__any_sync(0xffffffffu, ((screen0 | screen1) & 0x40000000u) != 0)) {
+        // exact fix-up for the K-tile(s) that failed the screen (rare): see fixup_tile
+        if (!corr_used) {
 #pragma unroll 1
-            for (int z = 0; z < kCols; ++z) { corr_raw[z + zero] = 0; corr_q[z + zero] = 0; }
-            corr_used = true;
-          }
-          fixup_tile(taddr, kCols, scale, p.int_bits, &corr_raw[zero], &corr_q[zero]);
+          for (int z = 0; z < kCols; ++z) { corr_raw[z + zero] = 0; corr_q[z + zero] = 0; }
+          corr_used = true;
         }
+        if (__any_sync(0xffffffffu, (screen0 & 0x40000000u) != 0))
+          fixup_tile(ta0, kCols, scale, p.int_bits, &corr_raw[zero], &corr_q[zero]);
+        if (__any_sync(0xffffffffu, (screen1 & 0x40000000u) != 0))
+          fixup_tile(ta1, kCols, scale, p.int_bits, &corr_raw[zero], &corr_q[zero]);
       }
       tc_fence_before();
       __syncwarp();
+      if (trole >= 0) trace(trole, gss, 1);
       if (lane == 0) mbar_arrive(tempty0 + 8u * grp);
+      if (trole >= 0) trace(trole, gss, 2);
+      ++gss;
       grp ^= 1; if (grp == 0) gphase ^= 1;
     }
     if (!ok) break;

@@ -108,6 +108,14 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 __device__ __forceinline__ void tmem_wait_ld() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+// The same wait, naming the registers a tcgen05.ld filled: later uses of them now depend on
+// the wait, so the compiler cannot schedule them ahead of it.
+__device__ __forceinline__ void tmem_wait_ld_regs(uint32_t (&r)[16]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+               :: "memory");
+}
 
 // Shared-memory matrix descriptor (sm_100 format): start address, leading / stride
 // byte offsets (all >> 4), version 1, 128-byte swizzle.
