@@ -14,17 +14,24 @@
 //     K-tiles cannot overflow int32; out-of-range addends go to per-thread side arrays
 //     in local memory that are touched only on that rare path.
 //
-// Tile 128 x BN.  Warps 0-1 = TMA producers, warp 2 = MMA issuer, then EPIW epilogue warps
-// (TMEM lane quarter x column group).  The single-lane roles are latency-bound: an
-// mbarrier probe, a tcgen05 fence, an MMA issue and a commit each take ~50-100 cycles,
-// i.e. ~600 cycles per smem stage for a producer and ~1000 per K-tile for the issuer
-// (measured with in-kernel clock traces).  Producer w therefore takes the stages with
-// index = w (mod 2); every index (stage, TMEM buffer, barrier phase) is a function of the
-// running stage / K-tile number, so the roles need no communication beyond the barriers.
-// Splitting the MMA issue over several warps the same way timed out on hardware and is
-// not used: one warp issues all MMAs, and the wide tile (BN = 256: 512 MMA cycles per
-// K-tile of 64) is what keeps its loop latency from dominating.
-// Persistent, optional split-K with integer atomics + last arriver.  All waits bounded.
+// Tile 128 x 128, one persistent CTA per SM.  Warp 0 = TMA producer, warp 1 = MMA issuer,
+// then 16 epilogue warps (TMEM lane quarter x 32-column group).  The single-lane roles are
+// latency-bound: an mbarrier probe, a tcgen05 fence, an MMA issue and a commit each take
+// 50-100 cycles of the issuing thread, so the pipeline hands over 128 of K at a time
+// ("super-stage": for k_tile 64 a pair of K-tiles into two TMEM buffers, each with a fresh
+// accumulator; for k_tile 128 one K-tile): one full/empty and one tensor-full/empty
+// hand-off per 8 MMAs.  Every index (stage, TMEM group, barrier phase) is a function of the
+// running super-stage number, so the roles need no communication beyond the barriers.
+//
+// Measured with the TRACE variant below (clock64 stamps of CTA 0) at 4096^3, k_tile 64:
+// a super-stage takes ~1700 cycles against 512 cycles of tensor work; the issuer spends
+// ~1250 of them between "operands landed" and "committed" (MMA issue is paced at 65-80
+// cycles per MMA when nothing else runs and ~125 when the 16 epilogue warps convert), the
+// rest waiting for the epilogue to hand the TMEM group back.  Tried and measured slower or
+// equal: two issuer warps (one per TMEM group; correct, -10 %), four single-buffer groups
+// for k_tile 128 (equal), software-pipelined or pairwise TMEM loads in the epilogue
+// (-6 % / -11 %), no TMA copies at all (equal: shared-memory bandwidth is not the limit).
+// Split-K: per-split integer partial planes, summed by the last arriver.  All waits bounded.
 #include <cuda.h>
 
 #include "fxp_common.cuh"
