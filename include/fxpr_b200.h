@@ -40,8 +40,7 @@ extern "C" {
 /* ---- gemm flags -------------------------------------------------------- */
 #define FXPR_GEMM_FORCE_PORTABLE 1  /* route to the CUDA-core kernel (sequential-k partials) */
 #define FXPR_GEMM_FORCE_EXACT_TC 2  /* tensor-core kernel with the plain cvt.rni epilogue */
-#define FXPR_GEMM_CHECK_SUMSQ    4  /* fast epilogue: range check by packed sum of squares */
-#define FXPR_GEMM_TILE_N256      8  /* fast route: 128x256 output tiles instead of 128x128 */
+#define FXPR_GEMM_TRACE           32 /* timing study: partials_out receives clock stamps of CTA 0 instead of partials */
 
 /* ---- attention flags --------------------------------------------------- */
 #define FXPR_ATTN_CAUSAL         1

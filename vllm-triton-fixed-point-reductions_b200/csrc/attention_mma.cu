@@ -21,6 +21,7 @@
 //     query row, so a token's bits are the same in any batch, block or split.
 //   * K/V pages are staged with 16-byte cp.async into XOR-swizzled shared memory.
 #include <cooperative_groups.h>
+#include <cstdlib>
 
 #include "attention_common.cuh"
 #include "fxp_common.cuh"
@@ -137,12 +138,12 @@ static int launch_mma(const AttnParams& p, const MmaAttnShape& sh, cudaStream_t 
   return check_launch("attention_mma");
 }
 
-template <typename T, int HD, int NW, bool ACC64, bool ROWS8>
+template <typename T, int HD, int NW, bool ACC64, bool ROWS8, int NSTAGE = 2, int MINB = 4>
 static int launch_decode(const AttnParams& p, const MmaAttnShape& sh, cudaStream_t s) {
   constexpr int kTileBytes = kTileN * HD * 2;
-  const size_t smem = (size_t)16 * HD * 2 + 2 * (size_t)kTileBytes + NW * 16 * 4 + NW * 16 * 8 +
+  const size_t smem = (size_t)16 * HD * 2 + NSTAGE * (size_t)kTileBytes + NW * 16 * 4 + NW * 16 * 8 +
                       (size_t)sh.stash_keys * stash_bytes_per_key(sh.stash_rows);
-  auto k = attn_decode_kernel<T, HD, NW, ACC64, ROWS8>;
+  auto k = attn_decode_kernel<T, HD, NW, ACC64, ROWS8, NSTAGE, MINB>;
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
   if (e != cudaSuccess) { set_last_error("attention_decode smem attribute", e); return FXPR_ERR_CUDA; }
   if (p.num_splits > 8) {
@@ -206,12 +207,19 @@ int attention_mma(const AttnParams& p_in, int dtype, int max_query_len, bool for
   const bool stash = small && (int64_t)sh.stash_keys * stash_bytes_per_key(sh.stash_rows) <= 150 * 1024;
   if (!stash) sh.stash_keys = 0;
   const bool acc64 = p.int_bits == 64;
+  static const int variant = getenv("FXPR_DECODE_VARIANT") ? atoi(getenv("FXPR_DECODE_VARIANT")) : 0;   // tuning study
   // fast second pass (same bits): scale <= 2^16, 32- or 64-bit sums, bounded tiles per CTA
   const bool fast = !force_exact && p.scale <= 65536.0f && (p.int_bits == 32 || p.int_bits == 64) &&
                     per_rank <= kFastMaxTiles;
 
 #define FXPR_ATTN(TT, HDV)                                                                      \
   do {                                                                                          \
+    if (small && stash && sh.stash_rows <= 8 && variant == 1 && acc64)                          \
+      return launch_decode<TT, HDV, 4, true, true, 3, 3>(p, sh, s);                             \
+    if (small && stash && sh.stash_rows <= 8 && variant == 2 && acc64)                          \
+      return launch_decode<TT, HDV, 4, true, true, 4, 2>(p, sh, s);                             \
+    if (small && stash && sh.stash_rows <= 8 && variant == 3 && acc64)                          \
+      return launch_decode<TT, HDV, 4, true, true, 3, 4>(p, sh, s);                             \
     if (small && stash && sh.stash_rows <= 8)                                                   \
       return acc64 ? launch_decode<TT, HDV, 4, true, true>(p, sh, s)                     \
                    : launch_decode<TT, HDV, 4, false, true>(p, sh, s);                   \

@@ -13,13 +13,12 @@
 
 // ROWS8: at most 8 of the 16 tile rows are real (e.g. one token x GQA group of 4): the
 // second half of every accumulator fragment is known to be masked and is skipped.
-template <typename T, int HD, int NW, bool ACC64, bool ROWS8>
-__global__ void __launch_bounds__(NW * 32, 4)
+template <typename T, int HD, int NW, bool ACC64, bool ROWS8, int NSTAGE = 2, int MINB = 4>
+__global__ void __launch_bounds__(NW * 32, MINB)
 attn_decode_kernel(const AttnParams p, const MmaAttnShape sh) {
   constexpr int RC = HD / 8;
   constexpr int NT = NW * 32;
   constexpr int kTileBytes = kTileN * HD * 2;
-  constexpr int NSTAGE = 2;                      // more resident CTAs beat a deeper pipeline here
   constexpr int JW = 8 / NW;                       // 8-key groups per warp in pass A
   constexpr int DW = HD / 8 / NW;                  // 8-wide head-dim groups per warp in pass B
   static_assert((NW == 2 || NW == 4 || NW == 8) && (HD / 8 / NW) % 2 == 0, "warps must divide the 8 key groups and the HD/16 pairs");

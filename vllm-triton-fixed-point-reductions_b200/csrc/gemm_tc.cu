@@ -414,7 +414,7 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, TcParams& p, 
 
 bool gemm_tc_fast_supported(const GemmArgs& g, int split_k);
 int gemm_tc_fast(const GemmArgs& g, TcParams& p, const CUtensorMap& ma, const CUtensorMap& mb,
-                 int bn, cudaStream_t s);
+                 cudaStream_t s);
 
 int gemm_tc(const GemmArgs& g, cudaStream_t s) {
   const int sms = tc_device_sms();
@@ -457,7 +457,7 @@ int gemm_tc(const GemmArgs& g, cudaStream_t s) {
   }
 
   if (!(g.flags & FXPR_GEMM_FORCE_EXACT_TC) && gemm_tc_fast_supported(g, p.split_k)) {
-    return gemm_tc_fast(g, p, ma, mb, (g.flags & FXPR_GEMM_TILE_N256) ? 256 : 128, s);
+    return gemm_tc_fast(g, p, ma, mb, s);
   }
 
   if (g.dtype == FXPR_BF16) {

@@ -302,12 +302,11 @@ bool gemm_tc_fast_supported(const GemmArgs& g, int split_k) {
 }
 
 int gemm_tc_fast(const GemmArgs& g, TcParams& p, const CUtensorMap& ma, const CUtensorMap& mb,
-                 int bn, cudaStream_t s) {
+                 cudaStream_t s) {
   const int sms = tc_device_sms();
   if (sms < 0) return FXPR_ERR_ARCH;
-  (void)bn;
   p.idesc = make_idesc(g.dtype == FXPR_BF16 ? 1 : 0, p.b_kmajor ? 0 : 1, 128, kBM);
-  const bool trace = (g.flags & 32) != 0 && p.partials != nullptr;   // timing study, see the kernel
+  const bool trace = (g.flags & FXPR_GEMM_TRACE) != 0 && p.partials != nullptr;   // timing study, see the kernel
   const bool dump = p.partials != nullptr && !trace;
 #define FXPR_FAST(TT)                                                                              \
   do {                                                                                             \

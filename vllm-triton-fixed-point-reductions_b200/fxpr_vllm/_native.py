@@ -32,7 +32,7 @@ DTYPE_CODE = {
 
 GEMM_FORCE_PORTABLE = 1
 GEMM_FORCE_EXACT_TC = 2
-GEMM_CHECK_SUMSQ = 4
+GEMM_TRACE = 32
 ATTN_CAUSAL = 1
 ATTN_FORCE_PORTABLE = 2
 ATTN_EXACT_CONVERT = 4
