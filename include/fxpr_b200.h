@@ -204,6 +204,28 @@ int fxpr_attention_static_scratch(
                    int int_bits, int frac_bits, int num_splits,
                    int32_t* status_word, void* stream);
 
+/*
+ * Decoder-layer element-wise steps around the attention call (no reductions).
+ *
+ * fxpr_rope_kv_write: qkv is [tokens, (q_heads + 2 kv_heads) * head_dim] (Q heads, K heads,
+ * V heads).  Rotate-half RoPE in fp32 with cos/sin tables [max_pos, head_dim / 2]; rotated Q
+ * goes to q_out [tokens, q_heads, head_dim], rotated K and V go into the paged cache at
+ * block_table[seq_ids[t], positions[t] / page_size], slot positions[t] % page_size.  The
+ * cache strides are in elements (block, K-to-V plane, slot, head).  Replaces vLLM's
+ * reshape_and_cache_flash call of fxpr_vllm/attention_backend.py:253-277 plus the RoPE op
+ * before it.
+ * fxpr_silu_mul: out[r, c] = silu(gate_up[r, c]) * gate_up[r, f + c] for a fused [rows, 2 f]
+ * activation (vLLM's SiluAndMul).
+ */
+int fxpr_rope_kv_write(const void* qkv, int dtype, const float* cos_table, const float* sin_table,
+                       const int64_t* positions, const int64_t* seq_ids,
+                       const int32_t* block_table, int64_t bt_stride, void* q_out,
+                       void* kv_cache, int64_t tokens, int q_heads, int kv_heads,
+                       int head_dim, int page_size, int64_t kv_sblock, int64_t kv_skv,
+                       int64_t kv_sslot, int64_t kv_shead, void* stream);
+int fxpr_silu_mul(const void* gate_up, int dtype, void* out, int64_t rows, int64_t f,
+                  void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -69,3 +69,29 @@ def test_graph_decode_equals_eager_decode():
     for step in range(4):
         got = b.replay_decode().clone()
         assert torch.equal(got.view(torch.int16), eager[step].view(torch.int16)), step
+
+
+def test_fused_rope_kv_write_equals_torch_path():
+    """The fused RoPE + KV-cache-write kernel against the same steps as torch ops: rotated Q and
+    the cache contents must agree bit for bit (separate multiply / subtract roundings on both
+    sides)."""
+    from fxpr_vllm._lib import rope_kv_write, silu_mul
+    cfg = DecoderConfig(hidden=512, ffn=1024, q_heads=8, kv_heads=4, head_dim=64, vocab=1024, layers=1)
+    m = LlamaDecoder(cfg, LocalGroup(1), "cuda", seed=3, max_seqs=3, max_len=96, fused_elementwise=False)
+    g = torch.Generator(device="cuda").manual_seed(5)
+    T = 3 * 37
+    qkv = torch.randn((T, (8 + 2 * 4) * 64), generator=g, device="cuda").to(cfg.dtype)
+    seq_ids = torch.arange(3, device="cuda").repeat_interleave(37)
+    pos = torch.arange(37, device="cuda").repeat(3) + 5
+    cache_a = m.shards[0].kv_cache[0]
+    cache_b = torch.zeros_like(cache_a)
+    q, k, v = qkv.split([8 * 64, 4 * 64, 4 * 64], dim=1)
+    q_ref = m._rope(q.reshape(T, 8, 64), pos)
+    m._write_kv(cache_a, m._rope(k.reshape(T, 4, 64), pos), v.reshape(T, 4, 64), seq_ids, pos)
+    q_got = rope_kv_write(qkv, m.cos, m.sin, pos, seq_ids, m.block_table, cache_b, 8, 4)
+    assert torch.equal(q_got.view(torch.int16), q_ref.view(torch.int16))
+    assert torch.equal(cache_b.view(torch.int16), cache_a.view(torch.int16))
+    gu = torch.randn((50, 2 * 1024), generator=g, device="cuda").to(cfg.dtype)
+    ref = (torch.nn.functional.silu(gu[:, :1024].float()) * gu[:, 1024:].float())
+    got = silu_mul(gu).float()
+    assert (got - ref).abs().max() <= 0.01 * ref.abs().max()

@@ -1,0 +1,117 @@
+// Element-wise steps either side of the attention kernel in a decoder layer, fused so that a
+// decode step is a dozen launches per layer instead of fifty:
+//
+//   fxpr_rope_kv_write  split a fused QKV activation, apply rotate-half RoPE to Q and K in
+//                       fp32, write Q to its own tensor and K/V straight into the paged
+//                       cache (num_blocks, 2, page, kv_heads, head_dim).  In the reference
+//                       plugin the cache write is vLLM's reshape_and_cache_flash
+//                       (fxpr_vllm/attention_backend.py:253-277) and RoPE a separate vLLM op.
+//   fxpr_silu_mul       act = silu(gate) * up on a fused [T, 2F] gate/up activation.
+//
+// No reductions here: every output element depends on one or two input elements, so these
+// kernels cannot affect batch / split / tensor-parallel invariance.
+#include "fxp_common.cuh"
+
+namespace fxpr {
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+rope_kv_write_kernel(const T* __restrict__ qkv, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                     const int64_t* __restrict__ pos, const int64_t* __restrict__ seq_ids,
+                     const int32_t* __restrict__ block_table, int64_t bt_stride, T* __restrict__ q_out,
+                     T* __restrict__ kv_cache, int q_heads, int kv_heads, int head_dim, int page,
+                     int64_t kv_sblock, int64_t kv_skv, int64_t kv_sslot, int64_t kv_shead) {
+  const int64_t tok = blockIdx.x;
+  const int half = head_dim / 2;
+  const int64_t p = pos[tok];
+  const int64_t blk = block_table[seq_ids[tok] * bt_stride + p / page];
+  const int64_t slot = p % page;
+  const T* row = qkv + tok * (int64_t)(q_heads + 2 * kv_heads) * head_dim;
+  const float* cs = cos_t + p * half;
+  const float* sn = sin_t + p * half;
+  T* kdst = kv_cache + blk * kv_sblock + slot * kv_sslot;
+  T* vdst = kdst + kv_skv;
+  const int rope_heads = q_heads + kv_heads;
+  // rotated heads: one (i, i + half) pair per item
+  for (int idx = threadIdx.x; idx < rope_heads * half; idx += blockDim.x) {
+    const int h = idx / half, i = idx % half;
+    const float x1 = to_f32<T>(row[h * head_dim + i]);
+    const float x2 = to_f32<T>(row[h * head_dim + half + i]);
+    const float c = cs[i], s = sn[i];
+    const T o1 = from_f32<T>(__fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, s)));
+    const T o2 = from_f32<T>(__fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, s)));
+    if (h < q_heads) {
+      T* d = q_out + (tok * q_heads + h) * (int64_t)head_dim;
+      d[i] = o1; d[half + i] = o2;
+    } else {
+      T* d = kdst + (int64_t)(h - q_heads) * kv_shead;
+      d[i] = o1; d[half + i] = o2;
+    }
+  }
+  // V heads: plain copy
+  const T* vrow = row + (int64_t)rope_heads * head_dim;
+  for (int idx = threadIdx.x; idx < kv_heads * head_dim; idx += blockDim.x) {
+    const int h = idx / head_dim, i = idx % head_dim;
+    vdst[(int64_t)h * kv_shead + i] = vrow[idx];
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t rows, int64_t f) {
+  const int64_t n = rows * f;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = idx / f, c = idx % f;
+    const float g = to_f32<T>(gu[r * 2 * f + c]);
+    const float u = to_f32<T>(gu[r * 2 * f + f + c]);
+    const float sg = __fdiv_rn(g, __fadd_rn(1.0f, expf(-g)));
+    out[idx] = from_f32<T>(__fmul_rn(sg, u));
+  }
+}
+
+}  // namespace fxpr
+
+using namespace fxpr;
+
+extern "C" int fxpr_rope_kv_write(const void* qkv, int dtype, const float* cos_table, const float* sin_table,
+                                  const int64_t* positions, const int64_t* seq_ids,
+                                  const int32_t* block_table, int64_t bt_stride, void* q_out, void* kv_cache,
+                                  int64_t tokens, int q_heads, int kv_heads, int head_dim, int page_size,
+                                  int64_t kv_sblock, int64_t kv_skv, int64_t kv_sslot, int64_t kv_shead,
+                                  void* stream) {
+  if (tokens < 0 || q_heads < 0 || kv_heads <= 0 || head_dim <= 0 || (head_dim & 1) || page_size <= 0)
+    return FXPR_ERR_BAD_ARG;
+  if (tokens == 0) return FXPR_OK;
+  if (!qkv || !cos_table || !sin_table || !positions || !seq_ids || !block_table || !q_out || !kv_cache)
+    return FXPR_ERR_BAD_ARG;
+  if (tokens > 0x7fffffffLL) return FXPR_ERR_BAD_ARG;
+  cudaStream_t s = (cudaStream_t)stream;
+#define FXPR_ROPE(TT)                                                                                  \
+  rope_kv_write_kernel<TT><<<(unsigned)tokens, 256, 0, s>>>(                                           \
+      (const TT*)qkv, cos_table, sin_table, positions, seq_ids, block_table, bt_stride, (TT*)q_out,    \
+      (TT*)kv_cache, q_heads, kv_heads, head_dim, page_size, kv_sblock, kv_skv, kv_sslot, kv_shead)
+  switch (dtype) {
+    case FXPR_BF16: FXPR_ROPE(__nv_bfloat16); break;
+    case FXPR_F16: FXPR_ROPE(__half); break;
+    case FXPR_F32: FXPR_ROPE(float); break;
+    default: return FXPR_ERR_UNSUPPORTED;
+  }
+#undef FXPR_ROPE
+  return check_launch("rope_kv_write");
+}
+
+extern "C" int fxpr_silu_mul(const void* gate_up, int dtype, void* out, int64_t rows, int64_t f, void* stream) {
+  if (rows < 0 || f < 0) return FXPR_ERR_BAD_ARG;
+  if (rows == 0 || f == 0) return FXPR_OK;
+  if (!gate_up || !out) return FXPR_ERR_BAD_ARG;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int64_t n = rows * f;
+  const unsigned grid = (unsigned)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+  switch (dtype) {
+    case FXPR_BF16: silu_mul_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, rows, f); break;
+    case FXPR_F16: silu_mul_kernel<__half><<<grid, 256, 0, s>>>((const __half*)gate_up, (__half*)out, rows, f); break;
+    case FXPR_F32: silu_mul_kernel<float><<<grid, 256, 0, s>>>((const float*)gate_up, (float*)out, rows, f); break;
+    default: return FXPR_ERR_UNSUPPORTED;
+  }
+  return check_launch("silu_mul");
+}

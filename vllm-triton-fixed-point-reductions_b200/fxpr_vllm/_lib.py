@@ -250,6 +250,46 @@ def log_softmax_fxp_run(x: torch.Tensor, fxp_frac_bits: int) -> torch.Tensor:
 
 
 # --------------------------------------------------------------------------
+# decoder-layer element-wise steps (no reference counterpart: vLLM ops there)
+# --------------------------------------------------------------------------
+
+def rope_kv_write(qkv, cos, sin, positions, seq_ids, block_table, kv_cache, q_heads, kv_heads):
+    """Split ``qkv`` [T, (q_heads + 2 kv_heads) * d], rotate Q and K, return Q [T, q_heads, d]
+    and write K, V into the paged ``kv_cache`` (num_blocks, 2, page, kv_heads, d)."""
+    T = qkv.shape[0]
+    d = kv_cache.shape[-1]
+    q = torch.empty((T, q_heads, d), device=qkv.device, dtype=qkv.dtype)
+    if T == 0:
+        return q
+    if not (qkv.is_contiguous() and cos.dtype == torch.float32 and sin.dtype == torch.float32
+            and positions.dtype == torch.int64 and seq_ids.dtype == torch.int64
+            and block_table.dtype == torch.int32 and kv_cache.dtype == qkv.dtype):
+        raise TypeError("rope_kv_write: contiguous qkv, fp32 tables, int64 positions / ids, int32 block table")
+    with _on_device(qkv):
+        st = nat.load().fxpr_rope_kv_write(
+            qkv.data_ptr(), nat.DTYPE_CODE[qkv.dtype], cos.data_ptr(), sin.data_ptr(),
+            positions.data_ptr(), seq_ids.data_ptr(), block_table.data_ptr(), block_table.stride(0),
+            q.data_ptr(), kv_cache.data_ptr(), T, q_heads, kv_heads, d, kv_cache.shape[2],
+            kv_cache.stride(0), kv_cache.stride(1), kv_cache.stride(2), kv_cache.stride(3),
+            nat.stream_ptr(qkv.device))
+    nat.check(st, "rope_kv_write")
+    return q
+
+
+def silu_mul(gate_up):
+    """``silu(gate) * up`` of a fused [rows, 2 f] activation."""
+    rows, two_f = gate_up.shape
+    out = torch.empty((rows, two_f // 2), device=gate_up.device, dtype=gate_up.dtype)
+    if out.numel():
+        gu = gate_up.contiguous()
+        with _on_device(gu):
+            st = nat.load().fxpr_silu_mul(gu.data_ptr(), nat.DTYPE_CODE[gu.dtype], out.data_ptr(), rows,
+                                          two_f // 2, nat.stream_ptr(gu.device))
+        nat.check(st, "silu_mul")
+    return out
+
+
+# --------------------------------------------------------------------------
 # GEMM
 # --------------------------------------------------------------------------
 

@@ -25,7 +25,7 @@ import torch
 import torch.distributed as dist
 
 from . import library_ops as ops
-from ._lib import BLOCK_K_BY_DTYPE
+from ._lib import BLOCK_K_BY_DTYPE, rope_kv_write, silu_mul
 from .config import get_runtime_config
 from .tp import check_shardable
 
@@ -105,8 +105,10 @@ class _Shard:
 
 class LlamaDecoder:
     def __init__(self, cfg: DecoderConfig, group, device, *, seed: int = 0, max_seqs: int = 64,
-                 max_len: int = 1280):
+                 max_len: int = 1280, fused_elementwise: bool = True):
         self.cfg, self.group, self.device = cfg, group, torch.device(device)
+        # fused CUDA kernels for RoPE + KV-cache write and SiLU*mul, or the same steps as torch ops
+        self.fused = fused_elementwise
         tp = group.size
         if cfg.q_heads % tp or cfg.kv_heads % tp or cfg.ffn % tp or cfg.vocab % tp:
             raise ValueError(f"tp={tp} does not divide the head / ffn / vocab sizes")
@@ -194,10 +196,14 @@ class LlamaDecoder:
             outs = []
             for sh in shards:
                 qkv = ops.gemm_fxp(h, sh.qkv[layer], None, c.int_bits, c.frac_bits)
-                q, k, v = qkv.split([self.qh * hd, self.kvh * hd, self.kvh * hd], dim=1)
-                q = self._rope(q.reshape(T, self.qh, hd), pos)
-                k = self._rope(k.reshape(T, self.kvh, hd), pos)
-                self._write_kv(sh.kv_cache[layer], k, v.reshape(T, self.kvh, hd), seq_ids, pos)
+                if self.fused:
+                    q = rope_kv_write(qkv, self.cos, self.sin, pos, seq_ids, self.block_table,
+                                      sh.kv_cache[layer], self.qh, self.kvh)
+                else:
+                    q, k, v = qkv.split([self.qh * hd, self.kvh * hd, self.kvh * hd], dim=1)
+                    q = self._rope(q.reshape(T, self.qh, hd), pos)
+                    k = self._rope(k.reshape(T, self.kvh, hd), pos)
+                    self._write_kv(sh.kv_cache[layer], k, v.reshape(T, self.kvh, hd), seq_ids, pos)
                 o = torch.empty_like(q)
                 ops.unified_attention_fxp(q, sh.kv_cache[layer], o, qsl, seq_lens, bt, max_q, None, True,
                                           None, c.int_bits, c.frac_bits, 0.0, 0, 0)
@@ -207,8 +213,11 @@ class LlamaDecoder:
             acts = []
             for sh in shards:
                 gu = ops.gemm_fxp(h, sh.gate_up[layer], None, c.int_bits, c.frac_bits)
-                f = gu.shape[1] // 2
-                acts.append((torch.nn.functional.silu(gu[:, :f].float()) * gu[:, f:].float()).to(c.dtype))
+                if self.fused:
+                    acts.append(silu_mul(gu))
+                else:
+                    f = gu.shape[1] // 2
+                    acts.append((torch.nn.functional.silu(gu[:, :f].float()) * gu[:, f:].float()).to(c.dtype))
             x = self._row_parallel(acts, [sh.down[layer] for sh in shards])
         h = ops.rms_norm_fxp_residual(x, residual, self.norm_w[2 * c.layers], c.eps)
         last = h[(qsl[1:] - 1).long()]
