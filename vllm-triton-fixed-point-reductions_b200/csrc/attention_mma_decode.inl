@@ -84,38 +84,53 @@ attn_decode_kernel(const AttnParams p, const MmaAttnShape sh) {
 
   const T* kbase = (const T*)p.k + (int64_t)kvh * p.kv_shead;
   const T* vbase = (const T*)p.v + (int64_t)kvh * p.kv_shead;
-  // Staging one 64-key tile of K or V costs a handful of instructions per 16-byte copy:
-  // the thread's chunk column, its two row offsets inside a 16-key page group and its
-  // swizzled shared-memory offset are fixed; lanes 0-3 look the four page groups up in the
-  // block table and the warp shares them.  Rows past the sequence are zero-filled and never
-  // touch the block table.
-  constexpr int CPT = kTileN * RC / NT;            // copies per thread per tile
-  constexpr int KSTEP = NT / RC;                   // keys between a thread's consecutive copies
-  static_assert(16 % KSTEP == 0 || KSTEP % 16 == 0, "a thread's copies must map to whole page groups");
-  const int my_c = threadIdx.x % RC;
-  const int my_key0 = threadIdx.x / RC;            // < KSTEP
-  const uint32_t my_dst = swz<RC>(my_key0, my_c);  // (key0 + it*KSTEP) keeps key & 7 when KSTEP % 8 == 0
+  // Every warp stages exactly the shared-memory bytes it will read itself, so the main loops
+  // need no CTA-wide barrier: a warp waits for its own cp.async groups and runs ahead of (or
+  // behind) its siblings.  Pass A: warp w reads keys [16w, 16w+16) of a tile (all of the head
+  // dimension) -- one 16-key page group, one block-table entry.  Pass B: warp w reads all 64
+  // keys but only its HD/NW slice of the head dimension.  The tile layout in shared memory
+  // (64 rows x RC chunks, XOR swizzle) is the same in both passes.  Rows past the sequence
+  // are zero-filled and never touch the block table.
+  static_assert(NW == 4, "one 16-key page group per warp in pass A");
   const int pshift = sh.page_shift;
-  auto issue_tile = [&](const T* base, int t, uint32_t dst) {
-    int64_t my_off = -1;
+  auto page_offset = [&](int n) -> int64_t {         // element offset of key n's row (head 0)
+    const int blk = pshift >= 0 ? (n >> pshift) : n / p.page_size;
+    const int slot = pshift >= 0 ? (n & (p.page_size - 1)) : n % p.page_size;
+    return (int64_t)bt[blk] * p.kv_sblock + (int64_t)slot * p.kv_sslot;
+  };
+  constexpr int KCP = 16 * RC / 32;                  // copies per lane: 16 keys x RC chunks
+  const int ka_c = lane % RC, ka_key0 = lane / RC;   // pass A: chunk column, first key (step 32 / RC)
+  auto issue_k = [&](int t, uint32_t dst) {
+    const int n0 = t * kTileN + warp * 16;
+    const int n_left = seq_len - n0;                 // keys of this warp's group that exist
+    const int64_t off = n_left > 0 ? page_offset(n0) : 0;
+#pragma unroll
+    for (int it = 0; it < KCP; ++it) {
+      const int key = ka_key0 + it * (32 / RC);
+      const bool v = key < n_left;
+      const T* src = v ? kbase + off + (int64_t)key * p.kv_sslot + ka_c * 8 : kbase;
+      cp_async16(dst + swz<RC>(warp * 16 + key, ka_c), src, v);
+    }
+  };
+  constexpr int WC = RC / NW;                        // chunk columns per warp in pass B
+  constexpr int VCP = kTileN * WC / 32;              // copies per lane
+  const int vb_c = warp * WC + lane % WC, vb_key0 = lane / WC;
+  auto issue_v = [&](int t, uint32_t dst) {
+    int64_t my_off = 0;
     if (lane < 4) {
       const int n = t * kTileN + lane * 16;
-      if (n < seq_len) {
-        const int blk = pshift >= 0 ? (n >> pshift) : n / p.page_size;
-        const int slot = pshift >= 0 ? (n & (p.page_size - 1)) : n % p.page_size;
-        my_off = (int64_t)bt[blk] * p.kv_sblock + (int64_t)slot * p.kv_sslot;
-      }
+      if (n < seq_len) my_off = page_offset(n);
     }
     int64_t page_off[4];
 #pragma unroll
     for (int q4 = 0; q4 < 4; ++q4) page_off[q4] = __shfl_sync(0xffffffffu, my_off, q4);
-    const int n_left = seq_len - t * kTileN;       // keys of this tile that exist
+    const int n_left = seq_len - t * kTileN;
 #pragma unroll
-    for (int it = 0; it < CPT; ++it) {
-      const int key = my_key0 + it * KSTEP;
+    for (int it = 0; it < VCP; ++it) {
+      const int key = vb_key0 + it * (32 / WC);      // (32 / WC) divides 16: it selects the page group statically
       const bool v = key < n_left;
-      const T* src = v ? base + page_off[key >> 4] + (int64_t)(key & 15) * p.kv_sslot + my_c * 8 : base;
-      cp_async16(dst + my_dst + (uint32_t)(it * KSTEP * RC * 16), src, v);
+      const T* src = v ? vbase + page_off[(it * (32 / WC)) >> 4] + (int64_t)(key & 15) * p.kv_sslot + vb_c * 8 : vbase;
+      cp_async16(dst + swz<RC>(key, vb_c), src, v);
     }
   };
 
@@ -130,17 +145,19 @@ attn_decode_kernel(const AttnParams p, const MmaAttnShape sh) {
   // =============================== pass A =============================================
   float rmax[2] = {ninf, ninf};
   {
+    cp_async_wait<0>();
+    __syncthreads();                                 // Q is in shared memory for every warp
     int issued = t0;
 #pragma unroll 1
     for (int s = 0; s < NSTAGE - 1; ++s) {
-      if (issued < t1) { issue_tile(kbase, issued, stage0 + (issued - t0) % NSTAGE * kTileBytes); ++issued; }
+      if (issued < t1) { issue_k(issued, stage0 + (issued - t0) % NSTAGE * kTileBytes); ++issued; }
       cp_async_commit();
     }
 #pragma unroll 1
     for (int t = t0; t < t1; ++t) {
       cp_async_wait<NSTAGE - 2>();
-      __syncthreads();
-      if (issued < t1) { issue_tile(kbase, issued, stage0 + (issued - t0) % NSTAGE * kTileBytes); ++issued; }
+      __syncwarp();                                  // this warp's rows of tile t landed; its rows of t-1 are free
+      if (issued < t1) { issue_k(issued, stage0 + (issued - t0) % NSTAGE * kTileBytes); ++issued; }
       cp_async_commit();
       const uint32_t k_addr = stage0 + (t - t0) % NSTAGE * kTileBytes;
       float s[JW][4];
@@ -195,7 +212,7 @@ attn_decode_kernel(const AttnParams p, const MmaAttnShape sh) {
   int issued_b = t0;
 #pragma unroll 1
   for (int s = 0; s < NSTAGE - 1; ++s) {
-    if (issued_b < t1) { issue_tile(vbase, issued_b, stage0 + (issued_b - t0) % NSTAGE * kTileBytes); ++issued_b; }
+    if (issued_b < t1) { issue_v(issued_b, stage0 + (issued_b - t0) % NSTAGE * kTileBytes); ++issued_b; }
     cp_async_commit();
   }
   cluster.sync();                                    // also orders the stash writes before pass B
@@ -221,8 +238,8 @@ attn_decode_kernel(const AttnParams p, const MmaAttnShape sh) {
 #pragma unroll 1
     for (int t = t0; t < t1; ++t) {
       cp_async_wait<NSTAGE - 2>();
-      __syncthreads();
-      if (issued < t1) { issue_tile(vbase, issued, stage0 + (issued - t0) % NSTAGE * kTileBytes); ++issued; }
+      __syncwarp();
+      if (issued < t1) { issue_v(issued, stage0 + (issued - t0) % NSTAGE * kTileBytes); ++issued; }
       cp_async_commit();
       const uint32_t v_addr = stage0 + (t - t0) % NSTAGE * kTileBytes;
       uint32_t pa[4][4];
@@ -297,10 +314,15 @@ attn_decode_kernel(const AttnParams p, const MmaAttnShape sh) {
     }
   }
   cluster.sync();
-  if (rank == 0) {
+  {
+    // Every rank merges its own slice of the head dimension (integer sums over the ranks are
+    // order-free), so the peers' shared memory is needed only for a short, parallel read.
     const int rows_here = min(16, (tok_end - tok0) * G);
-    for (int idx = threadIdx.x; idx < rows_here * HD; idx += NT) {
-      const int r = idx / HD, d = idx % HD;
+    const int cpr = (HD + S - 1) / S;                // columns per rank
+    const int c0 = rank * cpr;
+    const int ncol = max(0, min(HD, c0 + cpr) - c0);
+    for (int idx = threadIdx.x; idx < rows_here * ncol; idx += NT) {
+      const int r = idx / ncol, d = c0 + idx % ncol;
       long long dsum = 0, wsum = 0;
       for (int rr = 0; rr < S; ++rr) {
         const long long* dp = cluster.map_shared_rank(den_s, rr);
