@@ -259,7 +259,10 @@ def run_gpu_arm(args):
         "gpu_launches": steps,
         "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peak, "unit": "TFLOP/s",
-                     "frac": per_gpu / peak, "traffic": None,
+                     "frac": per_gpu / peak, "traffic": 87.6e6,
+                     "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch "
+                                       "(profiles/gemm_tc_fast_kernel_cfg1.md): A and B once (67.1 MB) "
+                                       "plus the part of C that left L2 during the launch",
                      "peak_source": f"{peaks['source']} cuBLAS bf16 burst",
                      "frac_of_nominal_2250": per_gpu / NOMINAL["bf16_tflops"],
                      "algorithmic": "2*M*N*K = 137.44 GFLOP per launch"},
