@@ -40,6 +40,7 @@ extern "C" {
 /* ---- gemm flags -------------------------------------------------------- */
 #define FXPR_GEMM_FORCE_PORTABLE 1  /* route to the CUDA-core kernel (sequential-k partials) */
 #define FXPR_GEMM_FORCE_EXACT_TC 2  /* tensor-core kernel with the plain cvt.rni epilogue */
+#define FXPR_GEMM_NO_SKINNY      8  /* M <= 64: use the 128-row-tile kernel anyway (tests: same bits) */
 #define FXPR_GEMM_TRACE           32 /* timing study: partials_out receives clock stamps of CTA 0 instead of partials */
 
 /* ---- attention flags --------------------------------------------------- */

@@ -247,3 +247,42 @@ def test_b_given_as_transposed_weight_view():
     v1 = torch.ops.fxpr.gemm_fxp_int(a, w.t(), 64, 16)
     v2 = torch.ops.fxpr.gemm_fxp_int(a, w.t().contiguous(), 64, 16)
     assert torch.equal(v1, v2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("M", [1, 16, 33, 64])
+@pytest.mark.parametrize("kt,split", [(64, 1), (128, 1), (64, 3), (128, 4)])
+@pytest.mark.parametrize("int_bits", [32, 64])
+def test_decode_shape_kernel_equals_wide_tile_kernel(dtype, M, kt, split, int_bits):
+    """M <= 64 goes to the kernel that puts the weights on the 128-row side of the MMA.  Its
+    integers and outputs must be those of the 128-row-tile kernel (and hence do not depend on
+    how many rows share the launch), for both weight layouts, with bias, a ragged N and K,
+    split-K and partials outside the fast conversion's range."""
+    from fxpr_vllm import _native as nat
+
+    N, K = 520, 1096
+    a = _rand((M, K), dtype, 201).cuda()
+    b = _rand((K, N), dtype, 202, 0.05).cuda()
+    bias = _rand((N,), dtype, 203).cuda()
+    a[0, 5::7] = -3000.0
+    a[M - 1, :64] = 6.0e4
+    bt_view = b.t().contiguous().t()               # (K, N) view of an (N, K) row-major matrix
+    for bb in (b, bt_view):
+        with L.overrides(gemm_k_tile=kt, gemm_split_k=split):
+            sk_i = torch.ops.fxpr.gemm_fxp_int(a, bb, int_bits, 16)
+            sk_c = _gemm(a, bb, bias, int_bits, 16)
+        with L.overrides(gemm_k_tile=kt, gemm_split_k=1, gemm_flags=nat.GEMM_NO_SKINNY):
+            wide_i = torch.ops.fxpr.gemm_fxp_int(a, bb, int_bits, 16)
+            wide_c = _gemm(a, bb, bias, int_bits, 16)
+        assert torch.equal(sk_i, wide_i)
+        assert torch.equal(sk_c.view(torch.int16), wide_c.view(torch.int16))
+    L.check_device_status()
+
+
+def test_decode_row_bits_do_not_depend_on_the_batch():
+    """Row r of a 64-row launch (decode-shape kernel) equals row r of a 300-row launch."""
+    a = _rand((300, 1024), torch.bfloat16, 211).cuda()
+    b = _rand((1024, 384), torch.bfloat16, 212, 0.05).cuda()
+    big = _gemm(a, b, None, 64, 16)
+    small = _gemm(a[100:164].contiguous(), b, None, 64, 16)
+    assert torch.equal(small.view(torch.int16), big[100:164].view(torch.int16))

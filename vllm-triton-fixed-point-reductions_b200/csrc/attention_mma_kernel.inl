@@ -120,6 +120,36 @@ attn_mma_kernel(const AttnParams p, const MmaAttnShape sh) {
   const uint32_t qs_addr = smem_addr(q_s);
   const float ninf = -__int_as_float(0x7f800000);
 
+  // ldmatrix addresses: the XOR swizzle only depends on lane bits, so each fragment address is
+  // a per-lane base (a handful of variants selected by compile-time loop indices) plus a
+  // compile-time offset; nothing is recomputed per load.
+  const int r7 = lane & 7, l15 = lane & 15, c1 = lane >> 4;
+  uint32_t kbase_l[2];                              // K rows j*8 + r7, chunk (kk2*4 + (lane>>3)) ^ r7
+  {
+    const int lo = (lane >> 3) ^ (r7 & 3), hi = r7 >> 2;
+    const int base = (r7 * RC + lo) * 16;
+    kbase_l[0] = (uint32_t)(base + (hi ? 64 : 0));  // kk2 even
+    kbase_l[1] = (uint32_t)(base - (hi ? 64 : 0));  // kk2 odd
+  }
+  uint32_t qbase_l[2][2];                           // Q rows warp*16 + l15, chunk (kk2*4 + 2a + c1) ^ r7
+#pragma unroll
+  for (int par = 0; par < 2; ++par)
+#pragma unroll
+    for (int a2 = 0; a2 < 2; ++a2) {
+      const int lo = c1 ^ (r7 & 1), mid = a2 ^ ((r7 >> 1) & 1), hi = r7 >> 2;
+      qbase_l[par][a2] = (uint32_t)(((warp * 16 + l15) * RC + lo + 2 * mid) * 16 + (hi ? (par ? -64 : 64) : 0));
+    }
+  uint32_t vbase_l[4];                              // V rows kk*16 + l15, chunk (jn2*2 + c1) ^ r7
+#pragma unroll
+  for (int q = 0; q < 4; ++q)
+    vbase_l[q] = (uint32_t)((l15 * RC + (c1 ^ (r7 & 1))) * 16 + ((q ^ (r7 >> 1)) * 32));
+  // address of the V fragment for k-step kk (16 keys) and head-dim pair jn2
+  auto v_frag = [&](uint32_t v_addr, int kk, int jn2) -> uint32_t {
+    return v_addr + vbase_l[jn2 & 3] + (uint32_t)(kk * 16 * RC * 16 + (jn2 >> 2) * 128);
+  };
+
+  const bool plain_scores = !(p.cap_log2 > 0.0f) && p.alibi == nullptr;
+
   // scores of one tile for this warp's 16 rows: s[j][e], j = 8-key group, e = C-fragment slot
   auto qk_tile = [&](uint32_t k_addr, int t, float (&s)[8][4]) {
 #pragma unroll
@@ -127,17 +157,27 @@ attn_mma_kernel(const AttnParams p, const MmaAttnShape sh) {
 #pragma unroll
     for (int kk2 = 0; kk2 < HD / 32; ++kk2) {
       uint32_t a0[4], a1[4];
-      ldsm_x4(qs_addr + swz<RC>(warp * 16 + (lane & 15), kk2 * 4 + (lane >> 4)), a0[0], a0[1], a0[2], a0[3]);
-      ldsm_x4(qs_addr + swz<RC>(warp * 16 + (lane & 15), kk2 * 4 + 2 + (lane >> 4)), a1[0], a1[1], a1[2], a1[3]);
+      ldsm_x4(qs_addr + qbase_l[kk2 & 1][0] + kk2 * 64, a0[0], a0[1], a0[2], a0[3]);
+      ldsm_x4(qs_addr + qbase_l[kk2 & 1][1] + kk2 * 64, a1[0], a1[1], a1[2], a1[3]);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         uint32_t b0, b1, b2, b3;
-        ldsm_x4(k_addr + swz<RC>(j * 8 + (lane & 7), kk2 * 4 + (lane >> 3)), b0, b1, b2, b3);
+        ldsm_x4(k_addr + kbase_l[kk2 & 1] + (uint32_t)(j * 8 * RC * 16 + kk2 * 64), b0, b1, b2, b3);
         mma16816<T>(s[j], a0, b0, b1);
         mma16816<T>(s[j], a1, b2, b3);
       }
     }
-    // scale to log2 space, soft-cap, ALiBi, masks (attention.py:103-121, 249-254)
+    // scale to log2 space, soft-cap, ALiBi, masks (attention.py:103-121, 249-254).  A tile
+    // that lies inside the key range of all 16 rows of the warp needs the scale only.
+    const int tile_lo = t * kTileN, tile_hi = tile_lo + kTileN;
+    const bool inside = tile_lo >= max(r_kbeg[0], r_kbeg[1]) && tile_hi <= min(r_kend[0], r_kend[1]);
+    if (plain_scores && __all_sync(0xffffffffu, inside)) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[j][e] = __fmul_rn(s[j][e], p.ss_log2);
+      return;
+    }
 #pragma unroll
     for (int j = 0; j < 8; ++j)
 #pragma unroll

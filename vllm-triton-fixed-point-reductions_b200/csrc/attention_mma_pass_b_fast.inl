@@ -63,7 +63,7 @@
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
             uint32_t b0, b1, b2, b3;
-            ldsm_x4_t(v_addr + swz<RC>(kk * 16 + (lane & 15), jn2 * 2 + (lane >> 4)), b0, b1, b2, b3);
+            ldsm_x4_t(v_frag(v_addr, kk, jn2), b0, b1, b2, b3);
             mma16816<T>(pv0, pa[kk], b0, b1);
             mma16816<T>(pv1, pa[kk], b2, b3);
           }
@@ -91,7 +91,7 @@
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk) {
               uint32_t b0, b1, b2, b3;
-              ldsm_x4_t(v_addr + swz<RC>(kk * 16 + (lane & 15), jn2 * 2 + (lane >> 4)), b0, b1, b2, b3);
+              ldsm_x4_t(v_addr + swz<RC>(kk * 16 + (lane & 15), jn2 * 2 + (lane >> 4)), b0, b1, b2, b3);   // runtime jn2: no table lookup
               mma16816<T>(pv[0], pa[kk], b0, b1);
               mma16816<T>(pv[1], pa[kk], b2, b3);
             }

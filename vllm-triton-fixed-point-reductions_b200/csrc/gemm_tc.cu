@@ -413,6 +413,8 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, TcParams& p, 
 }
 
 bool gemm_tc_fast_supported(const GemmArgs& g, int split_k);
+bool gemm_tc_skinny_supported(const GemmArgs& g, int split_k);
+int gemm_tc_skinny(const GemmArgs& g, TcParams& p, const CUtensorMap& mw, cudaStream_t s);
 int gemm_tc_fast(const GemmArgs& g, TcParams& p, const CUtensorMap& ma, const CUtensorMap& mb,
                  cudaStream_t s);
 
@@ -456,6 +458,9 @@ int gemm_tc(const GemmArgs& g, cudaStream_t s) {
     p.acc_scratch = (char*)g.scratch + tc_lock_bytes(g.M, g.N);
   }
 
+  // decode shapes: weights on the 128-row side of the MMA (same bits, see gemm_tc_skinny.cu)
+  if (!(g.flags & (FXPR_GEMM_FORCE_EXACT_TC | FXPR_GEMM_NO_SKINNY)) && gemm_tc_skinny_supported(g, p.split_k))
+    return gemm_tc_skinny(g, p, mb, s);
   if (!(g.flags & FXPR_GEMM_FORCE_EXACT_TC) && gemm_tc_fast_supported(g, p.split_k)) {
     return gemm_tc_fast(g, p, ma, mb, s);
   }
