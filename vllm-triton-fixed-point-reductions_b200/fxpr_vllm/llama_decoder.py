@@ -173,6 +173,9 @@ class LlamaDecoder:
 
     def _row_parallel(self, acts, weights):
         c = self.cfg
+        if self.group.size == 1:
+            # nothing to exchange: the fused epilogue gives the same bits as int GEMM + epilogue
+            return ops.gemm_fxp(acts[0], weights[0], None, c.int_bits, c.frac_bits)
         accs = [ops.gemm_fxp_int(a, w, c.int_bits, c.frac_bits) for a, w in zip(acts, weights)]
         accs = self.group.all_reduce_int(accs)
         return ops.gemm_fxp_epilogue(accs[0], None, c.dtype, c.frac_bits)
