@@ -251,7 +251,7 @@ def test_b_given_as_transposed_weight_view():
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("M", [1, 16, 33, 64])
-@pytest.mark.parametrize("kt,split", [(64, 1), (128, 1), (64, 3), (128, 4)])
+@pytest.mark.parametrize("kt,split", [(64, 1), (128, 1), (64, 3), (128, 4), (64, 8), (128, 2), (64, 2)])
 @pytest.mark.parametrize("int_bits", [32, 64])
 def test_decode_shape_kernel_equals_wide_tile_kernel(dtype, M, kt, split, int_bits):
     """M <= 64 goes to the kernel that puts the weights on the 128-row side of the MMA.  Its
@@ -276,6 +276,10 @@ def test_decode_shape_kernel_equals_wide_tile_kernel(dtype, M, kt, split, int_bi
             wide_c = _gemm(a, bb, bias, int_bits, 16)
         assert torch.equal(sk_i, wide_i)
         assert torch.equal(sk_c.view(torch.int16), wide_c.view(torch.int16))
+        if split > 1:      # 2/4/8 splits merge inside a cluster by default; the scratch-plane merge must agree
+            with L.overrides(gemm_k_tile=kt, gemm_split_k=split, gemm_flags=nat.GEMM_NO_CLUSTER):
+                pl_i = torch.ops.fxpr.gemm_fxp_int(a, bb, int_bits, 16)
+            assert torch.equal(pl_i, wide_i)
     L.check_device_status()
 
 

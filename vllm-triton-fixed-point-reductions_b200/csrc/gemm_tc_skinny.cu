@@ -15,12 +15,15 @@
 // K-tile), rint-half-even conversion to Q-format on the FP32 pipe with the exact fix-up for
 // out-of-range partials, wrap-around integer sums; split-K through per-split partial planes.
 // An output element's bits do not depend on M, on the route or on the split count.
+#include <cooperative_groups.h>
 #include <cuda.h>
 
 #include "fxp_common.cuh"
 #include "gemm_common.cuh"
 #include "tc_common.cuh"
 #include "gemm_tc_fast_common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace fxpr {
 
@@ -32,7 +35,10 @@ static constexpr int kSkXBytes = 2 * kSkMP * kBK * 2;     // activations: two 64
 static constexpr int kSkSSBytes = kSkWBytes + kSkXBytes;  // 48 KB per super-stage
 static constexpr int kSkGroups = 8;                       // barrier slots (groups in use: 4 or 8)
 
-template <typename T>
+// CLUSTER: split-K as a thread-block cluster (grid = splits x tiles, one item per CTA): the
+// ranks leave their integer partials in their own shared memory and every rank sums a slice of
+// the rows over its peers through distributed shared memory -- no global scratch, no fences.
+template <typename T, bool CLUSTER>
 __global__ void __launch_bounds__(kSkWarps * 32, 1)
 gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_constant__ CUtensorMap tma_x,
                       const TcParams p, const int zero /* always 0: keeps the side arrays in local memory */) {
@@ -74,6 +80,10 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_co
 
   const int tiles_n = p.tiles_n;                         // 128-column tiles; one row tile (M <= 64)
   const int items = tiles_n * p.split_k;
+  // item = tile * split_k + split.  Persistent: CTA b takes items b, b + grid, ...  Cluster:
+  // CTA (x, y) takes the single item (tile y, split x).
+  const int first_item = CLUSTER ? (int)(blockIdx.y * p.split_k + blockIdx.x) : (int)blockIdx.x;
+  const int item_step = CLUSTER ? items : (int)gridDim.x;
   const int k_tiles_total = (p.K + p.k_tile - 1) / p.k_tile;
   const bool pairs = p.k_tile == 64;                     // two K-tiles per super-stage
   const int ngroup = pairs ? 4 : 8;
@@ -83,7 +93,7 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_co
     // ------------------------------ TMA producer --------------------------------
     const bool wk = p.b_kmajor != 0;                     // weights given as an (N, K) row-major view
     int stage = 0; uint32_t phase = 1;
-    for (int item = blockIdx.x; item < items; item += gridDim.x) {
+    for (int item = first_item; item < items; item += item_step) {
       const int n0 = (item / p.split_k) * 128;
       const int ks = item % p.split_k;
       const int n_kt = (k_tiles_total - ks + p.split_k - 1) / p.split_k;
@@ -124,7 +134,7 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_co
     constexpr uint64_t kHalfW = (kSkWBytes / 2) >> 4, kHalfX = (kSkXBytes / 2) >> 4;
     const uint32_t idesc = p.idesc;
     int stage = 0; uint32_t phase = 0; int grp = 0; uint32_t gphase = 1;
-    for (int item = blockIdx.x; item < items; item += gridDim.x) {
+    for (int item = first_item; item < items; item += item_step) {
       const int ks = item % p.split_k;
       const int n_kt = (k_tiles_total - ks + p.split_k - 1) / p.split_k;
       const int n_ss = pairs ? (n_kt + 1) >> 1 : n_kt;
@@ -161,6 +171,41 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_co
 #include "gemm_tc_skinny_epilogue.inl"
   }
 
+  if constexpr (CLUSTER) {
+    // ------------------------------ cluster merge ---------------------------------
+    // The epilogue warps left this split's integer partials in shared memory ([64 rows][128
+    // columns] int64 over the first stages, which no copy or MMA touches any more).  Rank r sums
+    // rows [r * 64 / S, (r + 1) * 64 / S) over all ranks and writes the outputs.  Every thread
+    // of every CTA reaches both cluster barriers, also after a timed-out wait.
+    cg::cluster_group cluster = cg::this_cluster();
+    __syncthreads();
+    cluster.sync();
+    if (warp >= 2 && !*abort_flag) {
+      const int S = p.split_k, rank = (int)blockIdx.x;
+      const long long* red = reinterpret_cast<const long long*>(smem_gen);
+      const int rows_per = MP / S, mr0 = rank * rows_per;
+      const int tile = (int)blockIdx.y;
+      const T* bias = (const T*)p.bias;
+      for (int idx = (int)threadIdx.x - 64; idx < rows_per * 128; idx += EPIW * 32) {
+        const int m = mr0 + idx / 128, nl = idx % 128, n = tile * 128 + nl;
+        if (m >= p.M || n >= p.N) continue;
+        long long q = 0;
+        for (int rr = 0; rr < S; ++rr) q += cluster.map_shared_rank(red, rr)[m * 128 + nl];
+        if (p.int_bits != 64) q = (long long)(int32_t)q;
+        if (p.c_int) {
+          if (p.int_bits == 64) ((long long*)p.c_int)[(int64_t)m * p.N + n] = q;
+          else ((int32_t*)p.c_int)[(int64_t)m * p.N + n] = (int32_t)q;
+        }
+        if (p.c) {
+          float v = fixed_to_float<long long>(q, p.inv_scale);
+          if (bias) v = __fadd_rn(v, to_f32<T>(bias[n]));
+          ((T*)p.c)[(int64_t)m * p.c_sm + n] = from_f32<T>(v);
+        }
+      }
+    }
+    cluster.sync();                                  // peers may still be reading this CTA's partials
+  }
+
   // ------------------------------ teardown ----------------------------------------
   tc_fence_before();
   __syncthreads();
@@ -186,9 +231,38 @@ bool gemm_tc_skinny_supported(const GemmArgs& g, int split_k) {
 }
 
 template <typename T>
+static int launch_skinny_cluster(const CUtensorMap& mw, const CUtensorMap& mx, TcParams& p, cudaStream_t s) {
+  constexpr int kSmem = kSkStages * kSkSSBytes + 256 + 1024;
+  auto k = gemm_tc_skinny_kernel<T, true>;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+    if (e != cudaSuccess) { set_last_error("gemm_tc_skinny smem attribute", e); return FXPR_ERR_CUDA; }
+    attr_done = true;
+  }
+  p.tiles_m = 1;
+  p.tiles_n = (p.N + 127) / 128;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)p.split_k, (unsigned)p.tiles_n, 1);
+  cfg.blockDim = dim3(kSkWarps * 32);
+  cfg.dynamicSmemBytes = kSmem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)p.split_k;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, k, mw, mx, p, 0);
+  if (e != cudaSuccess) { set_last_error("gemm_tc_skinny cluster launch", e); return FXPR_ERR_CUDA; }
+  return check_launch("gemm_tc_skinny");
+}
+
+template <typename T>
 static int launch_skinny(const CUtensorMap& mw, const CUtensorMap& mx, TcParams& p, int sms, cudaStream_t s) {
   constexpr int kSmem = kSkStages * kSkSSBytes + 256 + 1024;
-  auto k = gemm_tc_skinny_kernel<T>;
+  auto k = gemm_tc_skinny_kernel<T, false>;
   static bool attr_done = false;
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
@@ -214,6 +288,14 @@ int gemm_tc_skinny(const GemmArgs& g, TcParams& p, const CUtensorMap& mw, cudaSt
   }
   // M = 128 weight columns, N = 64 activation rows; bit 15: the 128-row operand is MN-major
   p.idesc = make_idesc(g.dtype == FXPR_BF16 ? 1 : 0, 0, kSkMP, 128) | (p.b_kmajor ? 0u : (1u << 15));
+  // 2, 4 or 8 splits run as a thread-block cluster (merge through distributed shared memory);
+  // other split counts use the partial planes in the caller's scratch.  Same bits either way.
+  const bool cluster = (p.split_k == 2 || p.split_k == 4 || p.split_k == 8) && (p.N + 127) / 128 <= 65535 &&
+                       !(g.flags & FXPR_GEMM_NO_CLUSTER);
+  if (cluster) {
+    if (g.dtype == FXPR_BF16) return launch_skinny_cluster<__nv_bfloat16>(mw, mx, p, s);
+    return launch_skinny_cluster<__half>(mw, mx, p, s);
+  }
   if (g.dtype == FXPR_BF16) return launch_skinny<__nv_bfloat16>(mw, mx, p, sms, s);
   return launch_skinny<__half>(mw, mx, p, sms, s);
 }

@@ -23,7 +23,7 @@
   long long corr_q[kCols];
   bool corr_used = false;
 
-  for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
+  for (int item = first_item; item < items && ok; item += item_step) {
     const int tile = item / p.split_k, ks = item % p.split_k;
     const int n = tile * 128 + n_in_tile;
     const int n_kt = (k_tiles_total - ks + p.split_k - 1) / p.split_k;
@@ -89,6 +89,16 @@
 
     // Split-K: per-split integer partial planes, column-major inside the 128 x 64 tile (the
     // warp's 32 output columns are 32 consecutive words); the last arriver adds the others.
+    if constexpr (CLUSTER) {
+      if (p.split_k > 1) {
+        // this split's partials go to shared memory; the cluster merge after the role branches
+        // sums them over the ranks and writes the outputs
+        long long* red = reinterpret_cast<long long*>(smem_gen);
+#pragma unroll
+        for (int i = 0; i < kCols; ++i) red[(m0 + i) * 128 + n_in_tile] = total(i);
+        continue;
+      }
+    }
     bool do_store = true;
     const int64_t plane_elems = (int64_t)128 * MP;
     const int64_t plane_stride = (int64_t)tiles_n * plane_elems;

@@ -33,6 +33,7 @@ DTYPE_CODE = {
 GEMM_FORCE_PORTABLE = 1
 GEMM_FORCE_EXACT_TC = 2
 GEMM_NO_SKINNY = 8
+GEMM_NO_CLUSTER = 16
 GEMM_TRACE = 32
 ATTN_CAUSAL = 1
 ATTN_FORCE_PORTABLE = 2
