@@ -21,7 +21,10 @@ rope_kv_write_kernel(const T* __restrict__ qkv, const float* __restrict__ cos_t,
                      const int32_t* __restrict__ block_table, int64_t bt_stride, T* __restrict__ q_out,
                      T* __restrict__ kv_cache, int q_heads, int kv_heads, int head_dim, int page,
                      int64_t kv_sblock, int64_t kv_skv, int64_t kv_sslot, int64_t kv_shead) {
+  // grid: (token, slice of the work): blockIdx.y strides over the head items so that a decode
+  // step (64 tokens) still fills the GPU
   const int64_t tok = blockIdx.x;
+  const int part = blockIdx.y, parts = gridDim.y;
   const int half = head_dim / 2;
   const int64_t p = pos[tok];
   const int64_t blk = block_table[seq_ids[tok] * bt_stride + p / page];
@@ -33,7 +36,7 @@ rope_kv_write_kernel(const T* __restrict__ qkv, const float* __restrict__ cos_t,
   T* vdst = kdst + kv_skv;
   const int rope_heads = q_heads + kv_heads;
   // rotated heads: one (i, i + half) pair per item
-  for (int idx = threadIdx.x; idx < rope_heads * half; idx += blockDim.x) {
+  for (int idx = part * blockDim.x + threadIdx.x; idx < rope_heads * half; idx += parts * blockDim.x) {
     const int h = idx / half, i = idx % half;
     const float x1 = to_f32<T>(row[h * head_dim + i]);
     const float x2 = to_f32<T>(row[h * head_dim + half + i]);
@@ -50,7 +53,7 @@ rope_kv_write_kernel(const T* __restrict__ qkv, const float* __restrict__ cos_t,
   }
   // V heads: plain copy
   const T* vrow = row + (int64_t)rope_heads * head_dim;
-  for (int idx = threadIdx.x; idx < kv_heads * head_dim; idx += blockDim.x) {
+  for (int idx = part * blockDim.x + threadIdx.x; idx < kv_heads * head_dim; idx += parts * blockDim.x) {
     const int h = idx / head_dim, i = idx % head_dim;
     vdst[(int64_t)h * kv_shead + i] = vrow[idx];
   }
@@ -86,8 +89,13 @@ extern "C" int fxpr_rope_kv_write(const void* qkv, int dtype, const float* cos_t
     return FXPR_ERR_BAD_ARG;
   if (tokens > 0x7fffffffLL) return FXPR_ERR_BAD_ARG;
   cudaStream_t s = (cudaStream_t)stream;
+  // enough CTAs for ~4 per SM at decode sizes, one per token for long prefills
+  const int work = (q_heads + kv_heads) * (head_dim / 2);
+  int parts = (work + 255) / 256;
+  while (parts > 1 && tokens * parts > 148 * 8) parts = (parts + 1) / 2;
+  const dim3 grid((unsigned)tokens, (unsigned)parts);
 #define FXPR_ROPE(TT)                                                                                  \
-  rope_kv_write_kernel<TT><<<(unsigned)tokens, 256, 0, s>>>(                                           \
+  rope_kv_write_kernel<TT><<<grid, 256, 0, s>>>(                                                       \
       (const TT*)qkv, cos_table, sin_table, positions, seq_ids, block_table, bt_stride, (TT*)q_out,    \
       (TT*)kv_cache, q_heads, kv_heads, head_dim, page_size, kv_sblock, kv_skv, kv_sslot, kv_shead)
   switch (dtype) {

@@ -250,7 +250,7 @@ class LlamaDecoder:
 
     @staticmethod
     def greedy(logits: torch.Tensor) -> torch.Tensor:
-        return logits.float().argmax(dim=-1)
+        return logits.argmax(dim=-1)        # exact in the io dtype: no float copy of [B, vocab]
 
     # ------------------------------------------------------------------ CUDA-graph decode
     def capture_decode(self, first_tokens: torch.Tensor, start_len: int):
