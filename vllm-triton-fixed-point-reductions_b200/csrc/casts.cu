@@ -14,41 +14,69 @@ struct alignas(sizeof(T) * N >= 16 ? 16 : sizeof(T) * N) Pack {
   T v[N];
 };
 
-// Each thread handles VEC consecutive elements per step.  VEC == 1 is the
+// Access shape: a lane moves E consecutive elements per access, chosen so that neither its
+// load nor its store exceeds 16 bytes, and the lanes of a warp are contiguous -- every load
+// and store instruction covers one unbroken span (fp32 -> int64: 256 B loads, 512 B stores).
+// U independent accesses per thread and step keep several loads in flight.  E == 1 is the
 // fallback for unaligned pointers.
-template <typename TIn, int BITS, int VEC>
+template <typename TIn, typename TOut>
+struct CastShape {
+  static constexpr int kIn = 16 / (int)sizeof(TIn), kOut = 16 / (int)sizeof(TOut);
+  static constexpr int E = kIn < kOut ? kIn : kOut;
+};
+static constexpr int kCastU = 4;
+
+template <typename TIn, int BITS, int E>
 __global__ void __launch_bounds__(kCastThreads)
 float_to_fixed_kernel(const TIn* __restrict__ x, typename IntOf<BITS>::type* __restrict__ y,
                       int64_t n, float scale) {
   using TOut = typename IntOf<BITS>::type;
-  const int64_t stride = (int64_t)gridDim.x * blockDim.x * VEC;
-  int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
-  for (; i + VEC <= n; i += stride) {
-    Pack<TIn, VEC> in = *reinterpret_cast<const Pack<TIn, VEC>*>(x + i);
-    Pack<TOut, VEC> out;
+  const int64_t per_block = (int64_t)blockDim.x * E * kCastU;
+  for (int64_t base = (int64_t)blockIdx.x * per_block; base < n; base += (int64_t)gridDim.x * per_block) {
+    Pack<TIn, E> in[kCastU];
 #pragma unroll
-    for (int j = 0; j < VEC; ++j) out.v[j] = float_to_fixed<BITS>(to_f32<TIn>(in.v[j]), scale);
-    *reinterpret_cast<Pack<TOut, VEC>*>(y + i) = out;
-  }
-  if (VEC > 1 && i < n) {  // ragged tail: at most one thread gets here
-    for (int64_t j = i; j < n; ++j) y[j] = float_to_fixed<BITS>(to_f32<TIn>(x[j]), scale);
+    for (int u = 0; u < kCastU; ++u) {
+      const int64_t i = base + ((int64_t)u * blockDim.x + threadIdx.x) * E;
+      if (i + E <= n) in[u] = *reinterpret_cast<const Pack<TIn, E>*>(x + i);
+    }
+#pragma unroll
+    for (int u = 0; u < kCastU; ++u) {
+      const int64_t i = base + ((int64_t)u * blockDim.x + threadIdx.x) * E;
+      if (i + E <= n) {
+        Pack<TOut, E> out;
+#pragma unroll
+        for (int j = 0; j < E; ++j) out.v[j] = float_to_fixed<BITS>(to_f32<TIn>(in[u].v[j]), scale);
+        *reinterpret_cast<Pack<TOut, E>*>(y + i) = out;
+      } else {
+        for (int64_t j = i; j < n; ++j) y[j] = float_to_fixed<BITS>(to_f32<TIn>(x[j]), scale);   // ragged tail
+      }
+    }
   }
 }
 
-template <typename TIn, typename TOut, int VEC>
+template <typename TIn, typename TOut, int E>
 __global__ void __launch_bounds__(kCastThreads)
 fixed_to_float_kernel(const TIn* __restrict__ x, TOut* __restrict__ y, int64_t n, float inv_scale) {
-  const int64_t stride = (int64_t)gridDim.x * blockDim.x * VEC;
-  int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
-  for (; i + VEC <= n; i += stride) {
-    Pack<TIn, VEC> in = *reinterpret_cast<const Pack<TIn, VEC>*>(x + i);
-    Pack<TOut, VEC> out;
+  const int64_t per_block = (int64_t)blockDim.x * E * kCastU;
+  for (int64_t base = (int64_t)blockIdx.x * per_block; base < n; base += (int64_t)gridDim.x * per_block) {
+    Pack<TIn, E> in[kCastU];
 #pragma unroll
-    for (int j = 0; j < VEC; ++j) out.v[j] = from_f32<TOut>(fixed_to_float<TIn>(in.v[j], inv_scale));
-    *reinterpret_cast<Pack<TOut, VEC>*>(y + i) = out;
-  }
-  if (VEC > 1 && i < n) {
-    for (int64_t j = i; j < n; ++j) y[j] = from_f32<TOut>(fixed_to_float<TIn>(x[j], inv_scale));
+    for (int u = 0; u < kCastU; ++u) {
+      const int64_t i = base + ((int64_t)u * blockDim.x + threadIdx.x) * E;
+      if (i + E <= n) in[u] = *reinterpret_cast<const Pack<TIn, E>*>(x + i);
+    }
+#pragma unroll
+    for (int u = 0; u < kCastU; ++u) {
+      const int64_t i = base + ((int64_t)u * blockDim.x + threadIdx.x) * E;
+      if (i + E <= n) {
+        Pack<TOut, E> out;
+#pragma unroll
+        for (int j = 0; j < E; ++j) out.v[j] = from_f32<TOut>(fixed_to_float<TIn>(in[u].v[j], inv_scale));
+        *reinterpret_cast<Pack<TOut, E>*>(y + i) = out;
+      } else {
+        for (int64_t j = i; j < n; ++j) y[j] = from_f32<TOut>(fixed_to_float<TIn>(x[j], inv_scale));
+      }
+    }
   }
 }
 
@@ -66,6 +94,7 @@ static int num_sms() {
 }
 
 static int cast_grid(int64_t n, int vec) {
+  vec *= kCastU;
   int64_t want = (n + (int64_t)kCastThreads * vec - 1) / ((int64_t)kCastThreads * vec);
   int64_t cap = (int64_t)num_sms() * kCastCtasPerSm;
   return (int)(want < cap ? (want < 1 ? 1 : want) : cap);
@@ -78,7 +107,7 @@ static bool aligned16(const void* a, const void* b) {
 template <typename TIn, int BITS>
 static int launch_f2x(const void* x, void* y, int64_t n, float scale, cudaStream_t s) {
   using TOut = typename IntOf<BITS>::type;
-  constexpr int VEC = 8;  // 16..64 B in, 16..64 B out per step: whole 128-bit accesses
+  constexpr int VEC = CastShape<TIn, TOut>::E;
   if (aligned16(x, y)) {
     float_to_fixed_kernel<TIn, BITS, VEC><<<cast_grid(n, VEC), kCastThreads, 0, s>>>(
         (const TIn*)x, (TOut*)y, n, scale);
@@ -101,7 +130,7 @@ static int dispatch_f2x(const void* x, void* y, int bits, int64_t n, float scale
 
 template <typename TIn, typename TOut>
 static int launch_x2f(const void* x, void* y, int64_t n, float inv, cudaStream_t s) {
-  constexpr int VEC = 8;
+  constexpr int VEC = CastShape<TIn, TOut>::E;
   if (aligned16(x, y)) {
     fixed_to_float_kernel<TIn, TOut, VEC><<<cast_grid(n, VEC), kCastThreads, 0, s>>>(
         (const TIn*)x, (TOut*)y, n, inv);
