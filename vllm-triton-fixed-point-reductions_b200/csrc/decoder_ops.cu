@@ -59,17 +59,40 @@ rope_kv_write_kernel(const T* __restrict__ qkv, const float* __restrict__ cos_t,
   }
 }
 
-template <typename T>
+template <typename T, int VEC>
+struct alignas(sizeof(T) * VEC) ActPack {
+  T v[VEC];
+};
+
+// VEC elements (16 bytes when aligned) per lane and access, lanes contiguous.
+template <typename T, int VEC>
 __global__ void __launch_bounds__(256)
 silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t rows, int64_t f) {
-  const int64_t n = rows * f;
+  const int64_t fv = f / VEC;                      // launcher guarantees f % VEC == 0
+  const int64_t n = rows * fv;
   for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t r = idx / f, c = idx % f;
-    const float g = to_f32<T>(gu[r * 2 * f + c]);
-    const float u = to_f32<T>(gu[r * 2 * f + f + c]);
-    const float sg = __fdiv_rn(g, __fadd_rn(1.0f, expf(-g)));
-    out[idx] = from_f32<T>(__fmul_rn(sg, u));
+    const int64_t r = idx / fv, c = (idx % fv) * VEC;
+    const ActPack<T, VEC> g = *reinterpret_cast<const ActPack<T, VEC>*>(gu + r * 2 * f + c);
+    const ActPack<T, VEC> u = *reinterpret_cast<const ActPack<T, VEC>*>(gu + r * 2 * f + f + c);
+    ActPack<T, VEC> o;
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+      const float gf = to_f32<T>(g.v[j]);
+      const float sg = __fdiv_rn(gf, __fadd_rn(1.0f, expf(-gf)));
+      o.v[j] = from_f32<T>(__fmul_rn(sg, to_f32<T>(u.v[j])));
+    }
+    *reinterpret_cast<ActPack<T, VEC>*>(out + r * f + c) = o;
   }
+}
+
+template <typename T>
+static void launch_silu(const void* gu, void* out, int64_t rows, int64_t f, cudaStream_t s) {
+  constexpr int V = 16 / (int)sizeof(T);
+  const bool vec = (f % V == 0) && ((((uintptr_t)gu | (uintptr_t)out) & 15) == 0);
+  const int64_t n = rows * (vec ? f / V : f);
+  const unsigned grid = (unsigned)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+  if (vec) silu_mul_kernel<T, V><<<grid, 256, 0, s>>>((const T*)gu, (T*)out, rows, f);
+  else silu_mul_kernel<T, 1><<<grid, 256, 0, s>>>((const T*)gu, (T*)out, rows, f);
 }
 
 }  // namespace fxpr
@@ -113,12 +136,10 @@ extern "C" int fxpr_silu_mul(const void* gate_up, int dtype, void* out, int64_t 
   if (rows == 0 || f == 0) return FXPR_OK;
   if (!gate_up || !out) return FXPR_ERR_BAD_ARG;
   cudaStream_t s = (cudaStream_t)stream;
-  const int64_t n = rows * f;
-  const unsigned grid = (unsigned)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
   switch (dtype) {
-    case FXPR_BF16: silu_mul_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, rows, f); break;
-    case FXPR_F16: silu_mul_kernel<__half><<<grid, 256, 0, s>>>((const __half*)gate_up, (__half*)out, rows, f); break;
-    case FXPR_F32: silu_mul_kernel<float><<<grid, 256, 0, s>>>((const float*)gate_up, (float*)out, rows, f); break;
+    case FXPR_BF16: launch_silu<__nv_bfloat16>(gate_up, out, rows, f, s); break;
+    case FXPR_F16: launch_silu<__half>(gate_up, out, rows, f, s); break;
+    case FXPR_F32: launch_silu<float>(gate_up, out, rows, f, s); break;
     default: return FXPR_ERR_UNSUPPORTED;
   }
   return check_launch("silu_mul");
