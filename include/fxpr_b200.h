@@ -42,7 +42,9 @@ extern "C" {
 #define FXPR_GEMM_FORCE_EXACT_TC 2  /* tensor-core kernel with the plain cvt.rni epilogue */
 #define FXPR_GEMM_NO_SKINNY      8  /* M <= 64: use the 128-row-tile kernel anyway (tests: same bits) */
 #define FXPR_GEMM_NO_CLUSTER     16 /* M <= 64 split-K: partial planes in the scratch instead of a cluster merge (tests) */
-#define FXPR_GEMM_TRACE           32 /* timing study: partials_out receives clock stamps of CTA 0 instead of partials */
+#define FXPR_GEMM_TRACE           32
+#define FXPR_GEMM_TILE_N256       64 /* force 128 x 256 output tiles (default at k_tile 128; same bits) */
+#define FXPR_GEMM_TILE_N128       128 /* force 128 x 128 output tiles (default at k_tile 64; same bits) */ /* timing study: partials_out receives clock stamps of CTA 0 instead of partials */
 
 /* ---- attention flags --------------------------------------------------- */
 #define FXPR_ATTN_CAUSAL         1

@@ -206,7 +206,8 @@ def test_tp_sharding_single_gpu_equals_unsharded():
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("int_bits", [32, 64])
 @pytest.mark.parametrize("kt,split", [(64, 1), (128, 1), (64, 3), (128, 2)])
-def test_fast_epilogue_equals_plain_conversion_with_outliers(dtype, int_bits, kt, split):
+@pytest.mark.parametrize("tile", ["n128", "n256"])
+def test_fast_epilogue_equals_plain_conversion_with_outliers(dtype, int_bits, kt, split, tile):
     """The magic-number epilogue with its exact fix-up gives the same integers as the
     tensor-core kernel that converts every partial with cvt.rni (saturating), including
     rows whose partials leave the fast range, saturate int32 or overflow the 32-bit sum."""
@@ -219,7 +220,8 @@ def test_fast_epilogue_equals_plain_conversion_with_outliers(dtype, int_bits, kt
     a[M - 1, 5::7] = -3000.0
     a[M // 2, :64] = 6.0e4
     a[7, 100] = float("inf") if int_bits == 32 else 5.0e4
-    with L.overrides(gemm_k_tile=kt, gemm_split_k=split):
+    shape_flag = nat.GEMM_TILE_N128 if tile == "n128" else nat.GEMM_TILE_N256   # both tile shapes, whatever the default
+    with L.overrides(gemm_k_tile=kt, gemm_split_k=split, gemm_flags=shape_flag):
         fast_i = torch.ops.fxpr.gemm_fxp_int(a, b, int_bits, 16)
         fast_c = _gemm(a, b, None, int_bits, 16)
     with L.overrides(gemm_k_tile=kt, gemm_split_k=1, gemm_flags=nat.GEMM_FORCE_EXACT_TC):

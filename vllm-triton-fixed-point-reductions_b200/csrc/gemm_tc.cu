@@ -414,6 +414,8 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, TcParams& p, 
 
 bool gemm_tc_fast_supported(const GemmArgs& g, int split_k);
 bool gemm_tc_skinny_supported(const GemmArgs& g, int split_k);
+bool gemm_tc_n256_supported(const GemmArgs& g, int split_k);
+int gemm_tc_n256(const GemmArgs& g, TcParams& p, const CUtensorMap& ma, const CUtensorMap& mb, cudaStream_t s);
 int gemm_tc_skinny(const GemmArgs& g, TcParams& p, const CUtensorMap& mw, cudaStream_t s);
 int gemm_tc_fast(const GemmArgs& g, TcParams& p, const CUtensorMap& ma, const CUtensorMap& mb,
                  cudaStream_t s);
@@ -461,6 +463,12 @@ int gemm_tc(const GemmArgs& g, cudaStream_t s) {
   // decode shapes: weights on the 128-row side of the MMA (same bits, see gemm_tc_skinny.cu)
   if (!(g.flags & (FXPR_GEMM_FORCE_EXACT_TC | FXPR_GEMM_NO_SKINNY)) && gemm_tc_skinny_supported(g, p.split_k))
     return gemm_tc_skinny(g, p, mb, s);
+  // 128 x 256 tiles: measured +6 % at k_tile 128 (two 64-deep stages per accumulator) and -12 %
+  // at k_tile 64 (one MMA group per hand-off with only two accumulators in TMEM), same bits;
+  // so they are the default for k_tile 128 only.  The flags force either shape.
+  const bool want_n256 = (g.flags & FXPR_GEMM_TILE_N256) || (g.k_tile == 128 && !(g.flags & FXPR_GEMM_TILE_N128));
+  if (want_n256 && !(g.flags & FXPR_GEMM_FORCE_EXACT_TC) && gemm_tc_n256_supported(g, p.split_k))
+    return gemm_tc_n256(g, p, ma, mb, s);
   if (!(g.flags & FXPR_GEMM_FORCE_EXACT_TC) && gemm_tc_fast_supported(g, p.split_k)) {
     return gemm_tc_fast(g, p, ma, mb, s);
   }

@@ -35,6 +35,8 @@ GEMM_FORCE_EXACT_TC = 2
 GEMM_NO_SKINNY = 8
 GEMM_NO_CLUSTER = 16
 GEMM_TRACE = 32
+GEMM_TILE_N256 = 64
+GEMM_TILE_N128 = 128
 ATTN_CAUSAL = 1
 ATTN_FORCE_PORTABLE = 2
 ATTN_EXACT_CONVERT = 4
