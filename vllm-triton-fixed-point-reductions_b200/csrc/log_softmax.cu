@@ -130,6 +130,104 @@ log_softmax_kernel(const T* __restrict__ x, float* __restrict__ y, int cols, int
   cluster.sync();
 }
 
+// Register-resident variant for slices of at most 32 elements per thread (a 128k-wide row
+// split over 16 CTAs is 31.3): the slice never touches shared memory, which removes three
+// shared-memory instructions per element and lets eight CTAs share an SM.  Same arithmetic in
+// the same per-element order-free form, hence the same bits as log_softmax_kernel.
+template <typename T, int VEC>
+__global__ void __launch_bounds__(kLsmThreads)
+log_softmax_reg_kernel(const T* __restrict__ x, float* __restrict__ y, int cols, int slice_len,
+                       float scale, float inv_scale, bool wide_q) {
+  constexpr int NV = 32 / VEC;                     // vector loads per thread
+  __shared__ long long red_i[32];
+  __shared__ float red_f[32];
+  __shared__ float xchg_max;        // read by peer CTAs
+  __shared__ long long xchg_sum;    // read by peer CTAs
+  __shared__ float bc_log;
+
+  cg::cluster_group cluster = cg::this_cluster();
+  const unsigned csize = cluster.num_blocks();
+  const unsigned crank = cluster.block_rank();
+  const int64_t row = blockIdx.x / csize;
+  const int begin = (int)crank * slice_len;
+  const int end = min(cols, begin + slice_len);
+  const int len = max(0, end - begin);
+  const T* xr = x + row * (int64_t)cols + begin;
+  float* yr = y + row * (int64_t)cols + begin;
+  const int nvec = len / VEC;                      // launcher guarantees len % VEC == 0
+  const float ninf = -__int_as_float(0x7f800000);
+
+  float vals[32];
+  float lmax = ninf;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int c = k * kLsmThreads + (int)threadIdx.x;
+    if (c < nvec) {
+      const LsPack<T, VEC> pk = *reinterpret_cast<const LsPack<T, VEC>*>(xr + c * VEC);
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) { vals[k * VEC + j] = to_f32<T>(pk.v[j]); lmax = fmaxf(lmax, vals[k * VEC + j]); }
+    } else {
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) vals[k * VEC + j] = ninf;
+    }
+  }
+  lmax = block_max_f32(lmax, red_f);
+  if (threadIdx.x == 0) xchg_max = lmax;
+  cluster.sync();
+  float gmax = ninf;
+  for (unsigned r = 0; r < csize; ++r) gmax = fmaxf(gmax, *cluster.map_shared_rank(&xchg_max, r));
+
+  // e is in [0, 1]: for frac_bits <= 21 its Q-format value is the low mantissa of
+  // fma(e, 2^f, 1.5 * 2^23) (exactly rint-half-even, as cvt.rni gives), so the raw bit patterns
+  // are summed in 32 bits and count * MAGIC is taken out once (at most 32 terms of <= 2^21).
+  unsigned long long acc = 0;
+  uint32_t acc32 = 0, cnt = 0;
+  const bool magic_ok = scale <= 2097152.0f;
+  const float magic = __uint_as_float(0x4B400000u);
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int c = k * kLsmThreads + (int)threadIdx.x;
+    if (c < nvec) {
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) {
+        const float e = exp2_det(__fmul_rn(__fsub_rn(vals[k * VEC + j], gmax), FXPR_LOG2E_F32));
+        if (magic_ok) acc32 += __float_as_uint(__fmaf_rn(e, scale, magic));
+        else if (wide_q) acc += (unsigned long long)float_to_fixed<64>(e, scale);
+        else acc += (unsigned long long)(long long)float_to_fixed<32>(e, scale);
+      }
+      cnt += VEC;
+    }
+  }
+  if (magic_ok) acc = (unsigned long long)(uint32_t)(acc32 - cnt * 0x4B400000u);
+  const long long lsum = block_sum_i64((long long)acc, red_i);
+  if (threadIdx.x == 0) xchg_sum = lsum;
+  cluster.sync();
+  if (threadIdx.x == 0) {
+    long long total = 0;
+    for (unsigned r = 0; r < csize; ++r) total += *cluster.map_shared_rank(&xchg_sum, r);
+    bc_log = log_det(fixed_to_float<long long>(total, inv_scale));
+  }
+  __syncthreads();
+  const float lg = bc_log;
+
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int c = k * kLsmThreads + (int)threadIdx.x;
+    if (c < nvec) {
+#pragma unroll
+      for (int j4 = 0; j4 < VEC / 4; ++j4) {
+        float4 o;
+        o.x = __fsub_rn(__fsub_rn(vals[k * VEC + j4 * 4 + 0], gmax), lg);
+        o.y = __fsub_rn(__fsub_rn(vals[k * VEC + j4 * 4 + 1], gmax), lg);
+        o.z = __fsub_rn(__fsub_rn(vals[k * VEC + j4 * 4 + 2], gmax), lg);
+        o.w = __fsub_rn(__fsub_rn(vals[k * VEC + j4 * 4 + 3], gmax), lg);
+        *reinterpret_cast<float4*>(yr + c * VEC + j4 * 4) = o;
+      }
+    }
+  }
+  cluster.sync();                                  // peers may still be reading the exchange slots
+}
+
 template <typename T>
 static int launch_lsm(const void* x, float* y, int64_t rows, int cols, float scale, float inv,
                       bool wide_q, cudaStream_t s) {
@@ -162,6 +260,19 @@ static int launch_lsm(const void* x, float* y, int64_t rows, int cols, float sca
 
   const T* xp = (const T*)x;
   cudaError_t e;
+  // slices of at most 32 elements per thread stay in registers (y rows are 16-byte aligned
+  // whenever x rows are: cols % V == 0 with V >= 4)
+  if (vec_ok && slice_len <= 32 * kLsmThreads && ((((uintptr_t)y) & 15) == 0) && cols % 4 == 0) {
+    auto k = log_softmax_reg_kernel<T, V>;
+    if (csize > 8) {
+      e = cudaFuncSetAttribute(k, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+      if (e != cudaSuccess) { set_last_error("log_softmax cluster attribute", e); return FXPR_ERR_CUDA; }
+    }
+    cfg.dynamicSmemBytes = 0;
+    e = cudaLaunchKernelEx(&cfg, k, xp, y, cols, slice_len, scale, inv, wide_q);
+    if (e != cudaSuccess) { set_last_error("log_softmax launch", e); return FXPR_ERR_CUDA; }
+    return check_launch("log_softmax");
+  }
 #define FXPR_LSM_LAUNCH(VV, CC)                                                              \
   do {                                                                                       \
     auto k = log_softmax_kernel<T, VV, CC>;                                                  \
