@@ -226,18 +226,50 @@ def run_gpu_arm(args):
         clocks = sample_clocks_under_load(gemm_step, local)
         L.check_device_status()
 
-        # end to end through the public op with pinned host buffers
+        # End to end through the public op with pinned host buffers: every step copies its
+        # A and B from the host and its C back.  Copies and the kernel run on three streams with
+        # two buffer sets, so step i's download and step i + 1's upload overlap step i's GEMM --
+        # all of them inside the timed region.
         ha, hb = sets[0][0].cpu().pin_memory(), sets[0][1].cpu().pin_memory()
-        hc = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+        hcs = [torch.empty((M, N), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+        das = [torch.empty_like(sets[0][0]) for _ in range(2)]
+        dbs = [torch.empty_like(sets[0][1]) for _ in range(2)]
+        s_in, s_cmp, s_out = (torch.cuda.Stream(device=dev) for _ in range(3))
+        ev_in = [torch.cuda.Event() for _ in range(2)]
+        ev_cmp = [torch.cuda.Event() for _ in range(2)]
+        ev_out = [torch.cuda.Event() for _ in range(2)]
 
         def e2e_step(i):
-            da = ha.to(dev, non_blocking=True)
-            db = hb.to(dev, non_blocking=True)
-            c = torch.ops.fxpr.gemm_fxp(da, db, None, GEMM["int_bits"], GEMM["frac_bits"])
-            hc.copy_(c, non_blocking=True)
+            k = i % 2
+            with torch.cuda.stream(s_in):
+                s_in.wait_event(ev_cmp[k])                 # the GEMM that last read this buffer set
+                das[k].copy_(ha, non_blocking=True)
+                dbs[k].copy_(hb, non_blocking=True)
+                ev_in[k].record(s_in)
+            with torch.cuda.stream(s_cmp):
+                s_cmp.wait_event(ev_in[k])
+                c = torch.ops.fxpr.gemm_fxp(das[k], dbs[k], None, GEMM["int_bits"], GEMM["frac_bits"])
+                ev_cmp[k].record(s_cmp)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_cmp[k])
+                s_out.wait_event(ev_out[k])                # the download that last wrote this host buffer
+                c.record_stream(s_out)
+                hcs[k].copy_(c, non_blocking=True)
+                ev_out[k].record(s_out)
 
-        e2e_steps = max(3, min(steps, 10))
-        sec_e2e = time_cuda(e2e_step, e2e_steps, 3, dist)
+        def e2e_run(n, first):
+            cur = torch.cuda.current_stream(dev)
+            for st in (s_in, s_cmp, s_out):
+                st.wait_stream(cur)
+            for i in range(n):
+                e2e_step(first + i)
+            for st in (s_in, s_cmp, s_out):
+                cur.wait_stream(st)
+
+        e2e_steps = max(4, min(steps, 10))
+        e2e_run(4, 0)
+        sec_e2e = time_cuda(lambda i: e2e_run(e2e_steps, 0) if i == 1 else None, 1, 1, dist)
+        hc = hcs[(e2e_steps - 1) % 2]
     e2e_ok = bool(torch.equal(hc, ref.cpu()))
 
     value = world * flops * steps / sec / 1e12
@@ -255,7 +287,9 @@ def run_gpu_arm(args):
         "invariance_checked": "split-K {1,2,4,8,16} x 2 repeats, identical bf16 outputs",
         "e2e": {"value": world * flops * e2e_steps / sec_e2e / 1e12, "unit": "TFLOP/s",
                 "h2d_bytes_per_step": ha.numel() * 2 + hb.numel() * 2,
-                "d2h_bytes_per_step": hc.numel() * 2, "matches_resident_run": e2e_ok},
+                "d2h_bytes_per_step": hc.numel() * 2, "matches_resident_run": e2e_ok,
+                "how": "uploads, GEMM and download of consecutive steps overlapped on three streams "
+                       "(two buffer sets); every step still moves all of its bytes"},
         "gpu_launches": steps,
         "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peak, "unit": "TFLOP/s",
