@@ -292,3 +292,33 @@ def test_decode_row_bits_do_not_depend_on_the_batch():
     big = _gemm(a, b, None, 64, 16)
     small = _gemm(a[100:164].contiguous(), b, None, 64, 16)
     assert torch.equal(small.view(torch.int16), big[100:164].view(torch.int16))
+
+
+def test_routes_agree_on_random_shapes():
+    """Seeded sweep over ragged shapes: whichever kernel the dispatcher picks (decode-shape,
+    128x128 or 128x256 tiles, cluster or plane split-K) must give the integers of the
+    tensor-core kernel with plain cvt.rni conversion, for both weight layouts."""
+    from fxpr_vllm import _native as nat
+
+    g = torch.Generator().manual_seed(2024)
+    for case in range(40):
+        M = int(torch.randint(1, 400, (1,), generator=g))
+        if case % 3 == 0:
+            M = int(torch.randint(1, 65, (1,), generator=g))
+        N = 8 * int(torch.randint(8, 130, (1,), generator=g))
+        K = 8 * int(torch.randint(8, 300, (1,), generator=g))
+        kt = (64, 128)[case % 2]
+        split = (1, 2, 3, 4, 8)[case % 5]
+        int_bits = (64, 32)[(case // 2) % 2]
+        dtype = (torch.bfloat16, torch.float16)[(case // 4) % 2]
+        a = _rand((M, K), dtype, 1000 + case).cuda()
+        b = _rand((K, N), dtype, 2000 + case, 0.05).cuda()
+        if case % 7 == 0:
+            a[M // 2, : min(64, K)] = 3.0e4
+        bb = b if case % 2 else b.t().contiguous().t()
+        with L.overrides(gemm_k_tile=kt, gemm_split_k=split):
+            got = torch.ops.fxpr.gemm_fxp_int(a, bb, int_bits, 16)
+        with L.overrides(gemm_k_tile=kt, gemm_split_k=1, gemm_flags=nat.GEMM_FORCE_EXACT_TC):
+            exp = torch.ops.fxpr.gemm_fxp_int(a, bb, int_bits, 16)
+        assert torch.equal(got, exp), (case, M, N, K, kt, split, int_bits, dtype)
+    L.check_device_status()
