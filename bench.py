@@ -422,6 +422,42 @@ def bench_others(dev, peaks, L, syn):
     res["float_to_fixed_i64"] = {"us": sec * 1e6, "GB/s": byts / sec / 1e9,
                                  "frac_hbm_measured": byts / sec / 1e9 / hbm}
 
+    # cfg1 at the reference's own K-tile (128): 128 x 256 output tiles
+    ga, gb = syn.gemm_inputs(device=dev)
+    with L.overrides(gemm_k_tile=128, gemm_split_k=1):
+        sec = t(lambda i: torch.ops.fxpr.gemm_fxp(ga, gb, None, 64, 16), steps=20, warm=5)
+    res["gemm_cfg1_ktile128"] = {"us": sec * 1e6, "TFLOP/s": 2.0 * 4096 ** 3 / sec / 1e12,
+                                 "frac_tensor_measured": 2.0 * 4096 ** 3 / sec / 1e12 / peaks["bf16_tflops"]}
+
+    # cfg4's decode GEMM shapes (M = 64, K-tile 128), kernel-only: 20 launches in a CUDA graph
+    def graph_us(fn, n=20, reps=5):
+        fn()
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            fn()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(n):
+                fn()
+        g.replay()
+        return time_cuda(lambda i: g.replay(), reps, 1) / (n * reps) * 1e6
+
+    shapes = {"qkv 64x6144x4096": (64, 6144, 4096), "o_proj 64x4096x4096": (64, 4096, 4096),
+              "gate_up 64x28672x4096": (64, 28672, 4096), "down 64x4096x14336": (64, 4096, 14336),
+              "lm_head 64x128256x4096": (64, 128256, 4096)}
+    dec = {}
+    for name, (m_, n_, k_) in shapes.items():
+        xa, wb = syn.gemm_inputs(m_, n_, k_, device=dev, seed=40)
+        with L.overrides(gemm_k_tile=128):
+            us = graph_us(lambda: torch.ops.fxpr.gemm_fxp(xa, wb, None, 64, 16))
+        dec[name] = {"us": us, "weights_GB/s": k_ * n_ * 2 / us / 1e3,
+                     "frac_hbm_measured": k_ * n_ * 2 / us / 1e3 / hbm}
+        del xa, wb
+    res["gemm_decode_shapes_cfg4"] = dec
+
     # cfg2: paged decode attention, batch 64, ctx U[512, 8192]
     lens = syn.decode_batch_lens()
     q, kv, qsl, sl, bt = syn.paged_attention_inputs(lens, [1] * len(lens), device=dev)

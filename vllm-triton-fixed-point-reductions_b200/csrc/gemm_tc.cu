@@ -398,7 +398,10 @@ template <typename T, int BN, bool ACC64, int STAGES>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, TcParams& p, int sms, cudaStream_t s) {
   using L = SmemLayout<BN, STAGES>;
   auto k = gemm_tc_kernel<T, BN, ACC64, STAGES>;
-  static bool attr_done = false;
+  static bool attr_done_dev[64] = {};            // function attributes are per device
+  int dev_id = 0;
+  cudaGetDevice(&dev_id);
+  bool& attr_done = attr_done_dev[dev_id & 63];
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
     if (e != cudaSuccess) { set_last_error("gemm_tc smem attribute", e); return FXPR_ERR_CUDA; }

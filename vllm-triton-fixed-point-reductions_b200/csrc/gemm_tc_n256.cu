@@ -193,7 +193,10 @@ template <typename T>
 static int launch_n256(const CUtensorMap& ma, const CUtensorMap& mb, TcParams& p, int sms, cudaStream_t s) {
   constexpr int kSmem = kWdStages * kWdStageBytes + 256 + 1024;
   auto k = gemm_tc_n256_kernel<T>;
-  static bool attr_done = false;
+  static bool attr_done_dev[64] = {};            // function attributes are per device
+  int dev_id = 0;
+  cudaGetDevice(&dev_id);
+  bool& attr_done = attr_done_dev[dev_id & 63];
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
     if (e != cudaSuccess) { set_last_error("gemm_tc_n256 smem attribute", e); return FXPR_ERR_CUDA; }

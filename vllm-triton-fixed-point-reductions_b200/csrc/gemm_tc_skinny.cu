@@ -234,7 +234,10 @@ template <typename T>
 static int launch_skinny_cluster(const CUtensorMap& mw, const CUtensorMap& mx, TcParams& p, cudaStream_t s) {
   constexpr int kSmem = kSkStages * kSkSSBytes + 256 + 1024;
   auto k = gemm_tc_skinny_kernel<T, true>;
-  static bool attr_done = false;
+  static bool attr_done_dev[64] = {};            // function attributes are per device
+  int dev_id = 0;
+  cudaGetDevice(&dev_id);
+  bool& attr_done = attr_done_dev[dev_id & 63];
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
     if (e != cudaSuccess) { set_last_error("gemm_tc_skinny smem attribute", e); return FXPR_ERR_CUDA; }
@@ -263,7 +266,10 @@ template <typename T>
 static int launch_skinny(const CUtensorMap& mw, const CUtensorMap& mx, TcParams& p, int sms, cudaStream_t s) {
   constexpr int kSmem = kSkStages * kSkSSBytes + 256 + 1024;
   auto k = gemm_tc_skinny_kernel<T, false>;
-  static bool attr_done = false;
+  static bool attr_done_dev[64] = {};            // function attributes are per device
+  int dev_id = 0;
+  cudaGetDevice(&dev_id);
+  bool& attr_done = attr_done_dev[dev_id & 63];
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
     if (e != cudaSuccess) { set_last_error("gemm_tc_skinny smem attribute", e); return FXPR_ERR_CUDA; }
