@@ -21,7 +21,6 @@
 //     query row, so a token's bits are the same in any batch, block or split.
 //   * K/V pages are staged with 16-byte cp.async into XOR-swizzled shared memory.
 #include <cooperative_groups.h>
-#include <cstdlib>
 
 #include "attention_common.cuh"
 #include "fxp_common.cuh"
@@ -207,19 +206,12 @@ int attention_mma(const AttnParams& p_in, int dtype, int max_query_len, bool for
   const bool stash = small && (int64_t)sh.stash_keys * stash_bytes_per_key(sh.stash_rows) <= 150 * 1024;
   if (!stash) sh.stash_keys = 0;
   const bool acc64 = p.int_bits == 64;
-  static const int variant = getenv("FXPR_DECODE_VARIANT") ? atoi(getenv("FXPR_DECODE_VARIANT")) : 0;   // tuning study
   // fast second pass (same bits): scale <= 2^16, 32- or 64-bit sums, bounded tiles per CTA
   const bool fast = !force_exact && p.scale <= 65536.0f && (p.int_bits == 32 || p.int_bits == 64) &&
                     per_rank <= kFastMaxTiles;
 
 #define FXPR_ATTN(TT, HDV)                                                                      \
   do {                                                                                          \
-    if (small && stash && sh.stash_rows <= 8 && variant == 1 && acc64)                          \
-      return launch_decode<TT, HDV, 4, true, true, 3, 3>(p, sh, s);                             \
-    if (small && stash && sh.stash_rows <= 8 && variant == 2 && acc64)                          \
-      return launch_decode<TT, HDV, 4, true, true, 4, 2>(p, sh, s);                             \
-    if (small && stash && sh.stash_rows <= 8 && variant == 3 && acc64)                          \
-      return launch_decode<TT, HDV, 4, true, true, 3, 4>(p, sh, s);                             \
     if (small && stash && sh.stash_rows <= 8)                                                   \
       return acc64 ? launch_decode<TT, HDV, 4, true, true>(p, sh, s)                     \
                    : launch_decode<TT, HDV, 4, false, true>(p, sh, s);                   \
