@@ -204,3 +204,31 @@ def test_fast_conversion_prefill_equals_exact_conversion(dtype, hq, hkv, d, int_
         with L.overrides(attn_flags=flags):
             outs.append(_h().run_attention(q, kv, qsl, sl, bt, mq, int_bits=int_bits, frac_bits=frac_bits))
     assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("kwargs", [dict(causal=False), dict(window=24), dict(window=100), dict(alibi=True),
+                                    dict(scale=0.05), dict(frac_bits=8), dict(softcap=20.0)])
+@pytest.mark.parametrize("splits", [1, 3])
+def test_tensor_core_route_feature_flags_close_to_oracle(dtype, kwargs, splits):
+    """Sliding window, ALiBi, soft-cap, non-causal, custom scale and Q8 on the tensor-core
+    kernels (decode and prefill rows in one batch), against the oracle evaluated with the
+    same non-sequential partials: one rounding step of the io dtype plus a few Q LSBs; and the
+    split count must not change a bit."""
+    q, kv, qsl, sl, bt, mq = _mixed_batch(dtype, 8, 2, 128, 16, 17, ctx=(300, 150, 70), qlens=(1, 40, 70))
+    kw = dict(kwargs)
+    alibi = None
+    if kw.pop("alibi", False):
+        alibi = torch.linspace(0.05, 0.4, 8) * orc.RCP_LN2
+    run = lambda s: _h().run_attention(q, kv, qsl, sl, bt, mq, int_bits=64, splits=s,
+                                       alibi=None if alibi is None else alibi.cuda(), **kw)
+    got = run(splits)
+    assert torch.equal(got.view(torch.int16), run(1).view(torch.int16))
+    exp = orc.attention_fxp(q.cpu(), kv.cpu(), qsl.cpu(), sl.cpu(), bt.cpu(), int_bits=64,
+                            alibi_slopes=alibi, is_causal=kw.get("causal", True),
+                            softmax_scale=kw.get("scale"), frac_bits=kw.get("frac_bits", 16),
+                            window_size=kw.get("window", 0), logit_softcap=kw.get("softcap", 0.0),
+                            sequential=False, exp2_fn=torch.exp2).float()
+    frac = kw.get("frac_bits", 16)
+    tol = (2.0 ** -7 if dtype == torch.bfloat16 else 2.0 ** -9) * 2 + 8 * 2.0 ** -frac
+    assert (got.float().cpu() - exp).abs().max().item() <= tol * max(1.0, float(exp.abs().max()))
