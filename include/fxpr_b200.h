@@ -42,9 +42,9 @@ extern "C" {
 #define FXPR_GEMM_FORCE_EXACT_TC 2  /* tensor-core kernel with the plain cvt.rni epilogue */
 #define FXPR_GEMM_NO_SKINNY      8  /* M <= 64: use the 128-row-tile kernel anyway (tests: same bits) */
 #define FXPR_GEMM_NO_CLUSTER     16 /* M <= 64 split-K: partial planes in the scratch instead of a cluster merge (tests) */
-#define FXPR_GEMM_TRACE           32
-#define FXPR_GEMM_TILE_N256       64 /* force 128 x 256 output tiles (default at k_tile 128; same bits) */
-#define FXPR_GEMM_TILE_N128       128 /* force 128 x 128 output tiles (default at k_tile 64; same bits) */ /* timing study: partials_out receives clock stamps of CTA 0 instead of partials */
+#define FXPR_GEMM_TILE_N256       64 /* force 128 x 256 output tiles (same bits) */
+#define FXPR_GEMM_TILE_N128       128 /* force 128 x 128 output tiles (same bits) */
+#define FXPR_GEMM_LEAN            256 /* experimental kernel gemm_tc_lean.cu (A/B timing, same bits) */
 
 /* ---- attention flags --------------------------------------------------- */
 #define FXPR_ATTN_CAUSAL         1
@@ -183,9 +183,13 @@ int fxpr_attention(const void* q, const void* k_cache, const void* v_cache, void
  * allocator on this path: a server that gave all of HBM to its KV cache, a C
  * caller without torch, a loop that must avoid cudaMalloc's implicit
  * synchronisation.  It calls no cudaMalloc/cudaFree and no allocating library.
- *   - Problems whose scratch need (fxpr_attention_scratch_bytes) exceeds the
- *     capacity are refused with FXPR_ERR_SCRATCH and a message in
- *     fxpr_last_error(); nothing is launched.
+ *   - Only the CUDA-core route uses scratch at all (fp32 inputs, head sizes
+ *     other than 64/128, pages that are not a multiple of 16 tokens, or
+ *     FXPR_ATTN_FORCE_PORTABLE); the tensor-core route merges its splits inside a
+ *     thread-block cluster and never touches the array, whatever the sizes.
+ *   - Calls on the CUDA-core route whose scratch need
+ *     (fxpr_attention_scratch_bytes) exceeds the capacity are refused with
+ *     FXPR_ERR_SCRATCH and a message in fxpr_last_error(); nothing is launched.
  *   - The first call on each device looks up the array's device address
  *     (cudaGetSymbolAddress, with that device current); make that first call
  *     before any stream capture.

@@ -61,7 +61,22 @@ extern "C" int fxpr_attention_static_scratch(
     int int_bits, int frac_bits, int num_splits, int32_t* status_word, void* stream) {
   void* scratch = nullptr;
   int64_t need = 0;
-  if (num_splits > 1 && total_q_tokens > 0 && num_heads > 0 && head_dim > 0) {
+  // Only the CUDA-core route of fxpr_attention touches scratch memory (its split path keeps
+  // per-split maxima, integer totals and arrival counters there); the tensor-core route
+  // merges its splits inside a thread-block cluster.  So decide the route first, with the
+  // rule fxpr_attention itself applies, and size, refuse and resolve the array only when
+  // the call will really use it.
+  bool uses_scratch = false;
+  if (num_splits > 1 && total_q_tokens > 0 && num_reqs > 0 && num_heads > 0 && num_kv_heads > 0 &&
+      head_dim > 0 && page_size > 0 && num_heads % num_kv_heads == 0) {
+    fxpr::AttnParams rp{};
+    rp.q = q; rp.k = k_cache; rp.v = v_cache;
+    rp.num_reqs = num_reqs; rp.num_heads = num_heads; rp.num_kv_heads = num_kv_heads;
+    rp.head_dim = head_dim; rp.page_size = page_size;
+    rp.q_st = q_st; rp.q_sh = q_sh; rp.kv_sblock = kv_sblock; rp.kv_sslot = kv_sslot; rp.kv_shead = kv_shead;
+    uses_scratch = (flags & FXPR_ATTN_FORCE_PORTABLE) || !fxpr::attention_mma_supported(rp, dtype);
+  }
+  if (uses_scratch) {
     need = fxpr::attn_scratch_layout(total_q_tokens, num_heads, head_dim, num_splits).total;
     if (need > kStaticScratchBytes) {
       char msg[200];

@@ -422,6 +422,9 @@ int gemm_tc_n256(const GemmArgs& g, TcParams& p, const CUtensorMap& ma, const CU
 int gemm_tc_skinny(const GemmArgs& g, TcParams& p, const CUtensorMap& mw, cudaStream_t s);
 int gemm_tc_fast(const GemmArgs& g, TcParams& p, const CUtensorMap& ma, const CUtensorMap& mb,
                  cudaStream_t s);
+bool gemm_tc_lean_supported(const GemmArgs& g, int split_k);
+int gemm_tc_lean(const GemmArgs& g, TcParams& p, const CUtensorMap& ma, const CUtensorMap& mb,
+                 int bn, cudaStream_t s);
 
 int gemm_tc(const GemmArgs& g, cudaStream_t s) {
   const int sms = tc_device_sms();
@@ -443,6 +446,7 @@ int gemm_tc(const GemmArgs& g, cudaStream_t s) {
   }
 
   TcParams p;
+  p.dbg = 0;
   p.bias = g.bias; p.c = g.c; p.c_int = g.c_int; p.partials = g.partials;
   p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K; p.c_sm = g.c_sm;
   p.k_tile = g.k_tile; p.int_bits = g.int_bits;
@@ -469,6 +473,12 @@ int gemm_tc(const GemmArgs& g, cudaStream_t s) {
   // 128 x 256 tiles: measured +6 % at k_tile 128 (two 64-deep stages per accumulator) and -12 %
   // at k_tile 64 (one MMA group per hand-off with only two accumulators in TMEM), same bits;
   // so they are the default for k_tile 128 only.  The flags force either shape.
+  if ((g.flags & FXPR_GEMM_LEAN) && !(g.flags & FXPR_GEMM_FORCE_EXACT_TC) && gemm_tc_lean_supported(g, p.split_k)) {
+    int bn = (g.N >= 256) ? 256 : 128;
+    if (g.flags & FXPR_GEMM_TILE_N128) bn = 128;
+    if ((g.flags & FXPR_GEMM_TILE_N256) && g.N >= 256) bn = 256;
+    return gemm_tc_lean(g, p, ma, mb, bn, s);
+  }
   const bool want_n256 = (g.flags & FXPR_GEMM_TILE_N256) || (g.k_tile == 128 && !(g.flags & FXPR_GEMM_TILE_N128));
   if (want_n256 && !(g.flags & FXPR_GEMM_FORCE_EXACT_TC) && gemm_tc_n256_supported(g, p.split_k))
     return gemm_tc_n256(g, p, ma, mb, s);

@@ -23,7 +23,7 @@
 // hand-off per 8 MMAs.  Every index (stage, TMEM group, barrier phase) is a function of the
 // running super-stage number, so the roles need no communication beyond the barriers.
 //
-// Measured with the TRACE variant below (clock64 stamps of CTA 0) at 4096^3, k_tile 64:
+// Measured with clock64 stamps of CTA 0 at 4096^3, k_tile 64:
 // a super-stage takes ~1700 cycles against 512 cycles of tensor work; the issuer spends
 // ~1250 of them between "operands landed" and "committed" (MMA issue is paced at 65-80
 // cycles per MMA when nothing else runs and ~125 when the 16 epilogue warps convert), the
@@ -47,7 +47,7 @@ static constexpr int kSSBytesA = 2 * kBM * kBK * 2;      // two 64-deep halves o
 // A "super-stage" is 128 deep in K: for k_tile = 128 it is one K-tile (one TMEM buffer),
 // for k_tile = 64 it is a PAIR of K-tiles whose accumulators go to the two buffers of a
 // TMEM group.  One full/empty hand-off and one tfull/tempty hand-off per super-stage.
-template <typename T, int BN, int EPIW, bool DUMP, bool TRACE>
+template <typename T, int BN, int EPIW, bool DUMP>
 __global__ void __launch_bounds__((kRoleWarps + EPIW) * 32, 1)
 gemm_tc_fast_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                     const TcParams p, const int zero /* always 0: keeps the side arrays in local memory */) {
@@ -88,14 +88,6 @@ gemm_tc_fast_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // TRACE (timing study only): CTA 0 records clock64 stamps of its first 64 super-stages
-  // into the buffer passed as `partials`: [role][super-stage][slot], 4 slots each.
-  auto trace = [&](int role, int idx, int slot) {
-    if constexpr (TRACE) {
-      if (blockIdx.x == 0 && lane_id() == 0 && idx < 64)
-        reinterpret_cast<long long*>(p.partials)[(role * 64 + idx) * 4 + slot] = clock64();
-    }
-  };
 
   const int tiles_mn = p.tiles_m * p.tiles_n;
   const int items = tiles_mn * p.split_k;
@@ -132,7 +124,6 @@ gemm_tc_fast_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           const int kb = pairs ? ka + p.split_k * 64 : ka + 64;
           const bool two = pairs ? (2 * ss + 1 < n_kt) : true;
           if (!__all_sync(0xffffffffu, mbar_wait(empty0 + 8u * stage, phase, abort_flag))) goto producer_done;
-          trace(0, gss, 0);
           const uint32_t fb = full0 + 8u * stage;
           const uint32_t sa = smem_base + stage * kSSBytes;
           const uint32_t sb = sa + kSSBytesA;
@@ -150,7 +141,6 @@ gemm_tc_fast_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
             }
           }
           __syncwarp();
-          trace(0, gss, 1);
           ++gss;
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -182,9 +172,7 @@ gemm_tc_fast_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           const bool two = pairs ? (2 * ss + 1 < n_kt) : true;
           {
             const bool r1 = mbar_wait(tempty0 + 8u * grp, gphase, abort_flag);
-            trace(1, gss, 0);
             const bool r2 = mbar_wait(full0 + 8u * stage, phase, abort_flag);
-            trace(1, gss, 1);
             if (!__all_sync(0xffffffffu, r1 && r2)) goto issuer_done;
           }
           tc_fence_after();
@@ -207,7 +195,6 @@ gemm_tc_fast_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           umma_commit(tfull0 + 8u * grp);              // accumulator(s) of this super-stage complete
           }
           __syncwarp();
-          trace(1, gss, 2);
           ++gss;
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
           grp ^= 1; if (grp == 0) gphase ^= 1;
@@ -235,10 +222,10 @@ gemm_tc_fast_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   }
 }
 
-template <typename T, int BN, int EPIW, bool DUMP, bool TRACE = false>
+template <typename T, int BN, int EPIW, bool DUMP>
 static int launch_fast(const CUtensorMap& ma, const CUtensorMap& mb, TcParams& p, int sms, cudaStream_t s) {
   constexpr int kSmem = 3 * (kSSBytesA + 2 * BN * kBK * 2) + 256 + 1024;
-  auto k = gemm_tc_fast_kernel<T, BN, EPIW, DUMP, TRACE>;
+  auto k = gemm_tc_fast_kernel<T, BN, EPIW, DUMP>;
   static bool attr_done_dev[64] = {};            // function attributes are per device
   int dev_id = 0;
   cudaGetDevice(&dev_id);
@@ -273,12 +260,10 @@ int gemm_tc_fast(const GemmArgs& g, TcParams& p, const CUtensorMap& ma, const CU
   const int sms = tc_device_sms();
   if (sms < 0) return FXPR_ERR_ARCH;
   p.idesc = make_idesc(g.dtype == FXPR_BF16 ? 1 : 0, p.b_kmajor ? 0 : 1, 128, kBM);
-  const bool trace = (g.flags & FXPR_GEMM_TRACE) != 0 && p.partials != nullptr;   // timing study, see the kernel
-  const bool dump = p.partials != nullptr && !trace;
+  const bool dump = p.partials != nullptr;
 #define FXPR_FAST(TT)                                                                              \
   do {                                                                                             \
     if (dump) return launch_fast<TT, 128, 16, true>(ma, mb, p, sms, s);                            \
-    if (trace) return launch_fast<TT, 128, 16, false, true>(ma, mb, p, sms, s);                    \
     return launch_fast<TT, 128, 16, false>(ma, mb, p, sms, s);                                     \
   } while (0)
   if (g.dtype == FXPR_BF16) FXPR_FAST(__nv_bfloat16);

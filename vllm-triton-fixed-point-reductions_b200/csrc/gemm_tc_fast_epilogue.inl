@@ -11,7 +11,6 @@
   const float scale = p.scale;
   int grp = 0; uint32_t gphase = 0; uint32_t epi_phase = 0; bool ok = true;
   int gss = 0;
-  const int trole = warp == 2 ? 2 : (warp == 5 ? 3 : -1);
   auto epi_sync = [&]() -> bool {   // bounded barrier over the epilogue warps only
     __syncwarp();
     if (lane == 0) mbar_arrive(epi_bar);
@@ -41,7 +40,6 @@
     const int n_ss = pairs ? (n_kt + 1) >> 1 : n_kt;
     for (int ss = 0; ss < n_ss; ++ss) {
       if (!warp_wait(tfull0 + 8u * grp, gphase, abort_flag, lane)) { ok = false; break; }
-      if (trole >= 0) trace(trole, gss, 0);
       tc_fence_after();
       const int nbuf = (pairs && 2 * ss + 1 < n_kt) ? 2 : 1;
       // Hot path: r = fma(p, 2^f, MAGIC) on the FP32 pipe, raw bit patterns added as
@@ -92,9 +90,7 @@
       }
       tc_fence_before();
       __syncwarp();
-      if (trole >= 0) trace(trole, gss, 1);
       if (lane == 0) mbar_arrive(tempty0 + 8u * grp);
-      if (trole >= 0) trace(trole, gss, 2);
       ++gss;
       grp ^= 1; if (grp == 0) gphase ^= 1;
     }

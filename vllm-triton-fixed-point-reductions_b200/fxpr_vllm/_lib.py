@@ -294,18 +294,38 @@ def silu_mul(gate_up):
 # --------------------------------------------------------------------------
 
 _gemm_scratch: dict[tuple[int, int], torch.Tensor] = {}
+_gemm_scratch_retired: list[torch.Tensor] = []
 
 
 def _get_gemm_scratch(device: torch.device, nbytes: int) -> torch.Tensor:
     """Persistent zero-initialised split-K scratch per device, grown on demand
     (the kernel re-zeroes what it used; gemm.py:86-107 of the reference keeps
-    one such buffer too).  Grow it before CUDA-graph capture (``warmup_gemm``)."""
+    one such buffer too).  ``warmup_gemm`` sizes it before CUDA-graph capture.
+    A buffer that was replaced stays alive, so graphs captured with it keep a
+    valid, still-zeroed counter region; growing *during* capture would allocate
+    and zero-fill inside the graph, so that is refused."""
     idx = device.index if device.index is not None else torch.cuda.current_device()
     cur = _gemm_scratch.get((idx, 0))
     if cur is None or cur.numel() < nbytes:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError(
+                f"gemm_fxp: split-K scratch of {nbytes} bytes needed during CUDA-graph capture but only "
+                f"{0 if cur is None else cur.numel()} are allocated; run the shape once (or warmup_gemm) "
+                "before capturing")
+        if cur is not None:
+            _gemm_scratch_retired.append(cur)
         cur = torch.zeros(max(nbytes, 1 << 20), device=device, dtype=torch.uint8)
         _gemm_scratch[(idx, 0)] = cur
     return cur
+
+
+def gemm_scratch_policy_bytes(num_sms: int, int_bits: int = 64) -> int:
+    """Largest scratch the automatic split-K policy (``pick_split_k``) can ask for,
+    whatever M, N and K: it doubles the split only while ``tiles * split * 2 <= num_sms``,
+    so at most ``num_sms`` integer partial tiles of 128 x 128 exist, each padded to 256
+    columns in the worst case, after the fixed 256 KiB counter region."""
+    planes = num_sms * 128 * 256 * (8 if int_bits == 64 else 4)
+    return 256 * 1024 + -(-planes // 256) * 256
 
 
 _status_words: dict[int, torch.Tensor] = {}

@@ -12,7 +12,19 @@ from pathlib import Path
 import torch
 
 _PKG_ROOT = Path(__file__).resolve().parent.parent
-LIB_PATH = Path(os.environ.get("FXPR_B200_LIB", _PKG_ROOT / "lib" / "libfxpr_b200.so"))
+
+
+def _find_lib() -> Path:
+    """``FXPR_B200_LIB`` if set, else a copy packaged beside this module (wheel
+    installs), else the in-tree build output ``../lib/``."""
+    env = os.environ.get("FXPR_B200_LIB")
+    if env:
+        return Path(env)
+    beside = Path(__file__).resolve().parent / "libfxpr_b200.so"
+    return beside if beside.exists() else _PKG_ROOT / "lib" / "libfxpr_b200.so"
+
+
+LIB_PATH = _find_lib()
 
 FXPR_OK = 0
 FXPR_ERR_BAD_ARG = -1
@@ -34,7 +46,7 @@ GEMM_FORCE_PORTABLE = 1
 GEMM_FORCE_EXACT_TC = 2
 GEMM_NO_SKINNY = 8
 GEMM_NO_CLUSTER = 16
-GEMM_TRACE = 32
+GEMM_LEAN = 256
 GEMM_TILE_N256 = 64
 GEMM_TILE_N128 = 128
 ATTN_CAUSAL = 1

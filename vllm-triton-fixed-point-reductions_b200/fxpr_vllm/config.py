@@ -5,6 +5,9 @@ names, defaults (Q16.16 in int32) and warn-and-fall-back behaviour.  Two extra,
 non-breaking knobs exist because the public ``gemm_fxp`` schema has no argument
 for them: ``FXPR_GEMM_KTILE`` (K-tile = conversion granularity; 0 keeps the
 reference's per-dtype default) and ``FXPR_GEMM_SPLIT_K`` (0 = automatic).
+``FXPR_DISABLE_SAMPLER=1`` keeps vLLM's own ``log_softmax`` in the sampler (the
+reference's README lists a sampler module but ships none, so this switch has no
+counterpart there).
 """
 from __future__ import annotations
 
@@ -39,6 +42,7 @@ class FxpRuntimeConfig:
     fxp_frac_bits: int = DEFAULT_FXP_FRAC_BITS
     enable_rms_norm: bool = True
     enable_lm_head: bool = True
+    enable_sampler: bool = True
     disable_attention_warmup: bool = False
     disable_gemm_warmup: bool = False
     disable_rms_norm_warmup: bool = False
@@ -63,6 +67,7 @@ def load_runtime_config() -> FxpRuntimeConfig:
         fxp_frac_bits=_validated("FXPR_FRAC_BITS", (8, 16, 32), DEFAULT_FXP_FRAC_BITS),
         enable_rms_norm=not _env_flag("FXPR_DISABLE_RMS_NORM"),
         enable_lm_head=not _env_flag("FXPR_DISABLE_LM_HEAD"),
+        enable_sampler=not _env_flag("FXPR_DISABLE_SAMPLER"),
         disable_attention_warmup=_env_flag("FXPR_DISABLE_ATTENTION_WARMUP"),
         disable_gemm_warmup=_env_flag("FXPR_DISABLE_GEMM_WARMUP"),
         disable_rms_norm_warmup=_env_flag("FXPR_DISABLE_RMS_NORM_WARMUP"),

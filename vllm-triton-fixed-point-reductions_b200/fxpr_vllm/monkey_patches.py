@@ -1,5 +1,6 @@
 """Hooks into vLLM: swap the RMSNorm class and register the attention backend
-under ``CUSTOM`` (what ``fxpr_vllm/monkey_patches.py:9-43`` of the reference does)."""
+under ``CUSTOM`` (what ``fxpr_vllm/monkey_patches.py:9-43`` of the reference does),
+and route the sampler's log-softmax through ``log_softmax_fxp``."""
 from __future__ import annotations
 
 import logging
@@ -38,3 +39,30 @@ def patch_attention_backend() -> None:
 
     register_backend(AttentionBackendEnum.CUSTOM,
                      class_path=f"{backend.__module__}.{backend.__qualname__}")
+
+
+def patch_sampler() -> None:
+    """``Sampler.compute_logprobs`` (vllm/v1/sample/sampler.py: ``logits.log_softmax(dim=-1,
+    dtype=float32)``, whose float sum over the vocabulary depends on the reduction order)
+    becomes the fixed-point log-softmax: exact row maximum, ``sum_i Q(exp(x_i - max))`` as
+    an integer sum, one ``log``.  CUDA logits only; anything else keeps vLLM's own code."""
+    import torch
+    from vllm.v1.sample.sampler import Sampler
+
+    from . import library_ops as ops
+    from .config import get_runtime_config
+
+    if getattr(Sampler.compute_logprobs, "_fxpr_patched", False):
+        return
+    original = Sampler.compute_logprobs
+    frac_bits = get_runtime_config().fxp_frac_bits
+    io_dtypes = (torch.float16, torch.bfloat16, torch.float32)
+
+    def compute_logprobs(logits: torch.Tensor) -> torch.Tensor:
+        if logits.is_cuda and logits.dtype in io_dtypes:
+            return ops.log_softmax_fxp(logits, frac_bits)
+        return original(logits)
+
+    compute_logprobs._fxpr_patched = True
+    compute_logprobs._fxpr_original = original
+    Sampler.compute_logprobs = staticmethod(compute_logprobs)

@@ -14,6 +14,7 @@ float all-reduce off, which is what makes TP=1/2/4/8 bit-identical.
 """
 from __future__ import annotations
 
+import logging
 from collections.abc import Sequence
 from typing import Any
 
@@ -31,6 +32,8 @@ from vllm.model_executor.utils import set_weight_attrs
 from .config import get_runtime_config
 from .library_ops import gemm_fxp
 from .warmup import warmup_gemm, warmup_rms_norm
+
+logger = logging.getLogger("fxpr_vllm")
 
 
 def _to_kn(weight: torch.Tensor) -> torch.Tensor:
@@ -72,14 +75,30 @@ class FixedPointLinearMethod(_FxpMethodBase):
 
     def _setup_tp(self, layer: nn.Module) -> None:
         """Row-parallel layers that vLLM would all-reduce in floating point are reduced
-        here in integers instead (bias is then added after the reduce on every rank)."""
+        here in integers instead (bias is then added after the reduce on every rank).
+
+        The integer reduce only gives TP-independent bits when every rank's K-shard is a
+        whole number of K-tiles (the union of the shards' tiles is then the TP=1 tile
+        set); a layer that does not shard that way keeps vLLM's float all-reduce, with a
+        warning, rather than silently producing TP-dependent results."""
         layer._fxp_int_reduce = False
         try:
             from vllm.model_executor.layers.linear import RowParallelLinear
         except Exception:
             return
-        if isinstance(layer, RowParallelLinear) and getattr(layer, "tp_size", 1) > 1 \
-                and getattr(layer, "reduce_results", False):
+        tp = getattr(layer, "tp_size", 1)
+        if isinstance(layer, RowParallelLinear) and tp > 1 and getattr(layer, "reduce_results", False):
+            from ._lib import BLOCK_K_BY_DTYPE
+            from .tp import check_shardable
+
+            k_tile = get_runtime_config().gemm_k_tile or BLOCK_K_BY_DTYPE[layer.weight_native.dtype]
+            k_total = getattr(layer, "input_size", layer.weight_native.shape[0] * tp)
+            try:
+                check_shardable(int(k_total), int(tp), int(k_tile))
+            except ValueError as exc:
+                logger.warning("fxpr_vllm: %s; this layer keeps vLLM's float all-reduce and its "
+                               "bits depend on the TP degree", exc)
+                return
             layer._fxp_int_reduce = True
             layer.reduce_results = False
 

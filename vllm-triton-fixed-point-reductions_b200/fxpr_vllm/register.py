@@ -33,5 +33,8 @@ def register() -> None:
         steps.append("RMSNorm")
     if cfg.enable_lm_head:
         steps.append("lm_head via gemm_fxp")
+    if cfg.enable_sampler:
+        monkey_patches.patch_sampler()
+        steps.append("sampler log-softmax")
     logger.info("registered: %s", ", ".join(steps))
     _done = True

@@ -37,5 +37,12 @@ def row_parallel_gemm(x_shard: torch.Tensor, w_shard: torch.Tensor, bias: torch.
     acc = int_gemm(x_shard, w_shard, fxp_int_bits, fxp_frac_bits)
     if group is not None or (dist.is_available() and dist.is_initialized()):
         if dist.get_world_size(group) > 1:
-            dist.all_reduce(acc, op=dist.ReduceOp.SUM, group=group)
+            if acc.dtype == torch.int16:
+                # NCCL has no 16-bit integer sum: reduce in int32 and wrap back to 16 bits,
+                # which equals a 16-bit wrap-around sum of the ranks' accumulators
+                wide = acc.to(torch.int32)
+                dist.all_reduce(wide, op=dist.ReduceOp.SUM, group=group)
+                acc = wide.to(torch.int16)
+            else:
+                dist.all_reduce(acc, op=dist.ReduceOp.SUM, group=group)
     return epilogue(acc, bias, x_shard.dtype, fxp_frac_bits)

@@ -17,8 +17,6 @@ from .config import get_runtime_config
 
 logger = logging.getLogger("fxpr_vllm")
 
-_MAX_WARM_M = 8192  # split-K is only ever chosen for M below a few thousand rows
-
 
 def _capturing() -> bool:
     try:
@@ -33,8 +31,10 @@ def warmup_gemm(weight_native: torch.Tensor, fxp_int_bits: int, fxp_frac_bits: i
     try:
         from . import _lib, _native
 
-        k, n = weight_native.shape
-        need = _native.load().fxpr_gemm_scratch_bytes(_MAX_WARM_M, n, fxp_int_bits, 2)
+        _native.load()
+        # sized from the split-K policy's own bound (tens of MB), not from N: a
+        # 128256-column lm_head must not pin gigabytes before the KV cache is sized
+        need = _lib.gemm_scratch_policy_bytes(_lib._sm_count(weight_native.device), fxp_int_bits)
         _lib._get_gemm_scratch(weight_native.device, int(need))
         _lib._status_word(weight_native.device)
     except Exception as exc:  # warm-up must never break serving
