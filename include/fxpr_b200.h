@@ -44,7 +44,7 @@ extern "C" {
 #define FXPR_GEMM_NO_CLUSTER     16 /* M <= 64 split-K: partial planes in the scratch instead of a cluster merge (tests) */
 #define FXPR_GEMM_TILE_N256       64 /* force 128 x 256 output tiles (same bits) */
 #define FXPR_GEMM_TILE_N128       128 /* force 128 x 128 output tiles (same bits) */
-#define FXPR_GEMM_LEAN            256 /* experimental kernel gemm_tc_lean.cu (A/B timing, same bits) */
+#define FXPR_GEMM_PAIR            512 /* two-SM kernel (gemm_tc_pair.cu): 256 x BN tiles on CTA pairs, tcgen05 cta_group::2; same bits, opt-in */
 
 /* ---- attention flags --------------------------------------------------- */
 #define FXPR_ATTN_CAUSAL         1

@@ -206,7 +206,7 @@ def test_tp_sharding_single_gpu_equals_unsharded():
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("int_bits", [32, 64])
 @pytest.mark.parametrize("kt,split", [(64, 1), (128, 1), (64, 3), (128, 2)])
-@pytest.mark.parametrize("tile", ["n128", "n256"])
+@pytest.mark.parametrize("tile", ["n128", "n256", "pair128", "pair256"])
 def test_fast_epilogue_equals_plain_conversion_with_outliers(dtype, int_bits, kt, split, tile):
     """The magic-number epilogue with its exact fix-up gives the same integers as the
     tensor-core kernel that converts every partial with cvt.rni (saturating), including
@@ -220,7 +220,10 @@ def test_fast_epilogue_equals_plain_conversion_with_outliers(dtype, int_bits, kt
     a[M - 1, 5::7] = -3000.0
     a[M // 2, :64] = 6.0e4
     a[7, 100] = float("inf") if int_bits == 32 else 5.0e4
-    shape_flag = nat.GEMM_TILE_N128 if tile == "n128" else nat.GEMM_TILE_N256   # both tile shapes, whatever the default
+    # every tile shape, whatever the default: 128 x 128, 128 x 256, and the two-SM kernel's
+    # 256 x 128 / 256 x 256 pair tiles
+    shape_flag = {"n128": nat.GEMM_TILE_N128, "n256": nat.GEMM_TILE_N256,
+                  "pair128": nat.GEMM_PAIR | nat.GEMM_TILE_N128, "pair256": nat.GEMM_PAIR}[tile]
     with L.overrides(gemm_k_tile=kt, gemm_split_k=split, gemm_flags=shape_flag):
         fast_i = torch.ops.fxpr.gemm_fxp_int(a, b, int_bits, 16)
         fast_c = _gemm(a, b, None, int_bits, 16)
@@ -321,4 +324,36 @@ def test_routes_agree_on_random_shapes():
         with L.overrides(gemm_k_tile=kt, gemm_split_k=1, gemm_flags=nat.GEMM_FORCE_EXACT_TC):
             exp = torch.ops.fxpr.gemm_fxp_int(a, bb, int_bits, 16)
         assert torch.equal(got, exp), (case, M, N, K, kt, split, int_bits, dtype)
+    L.check_device_status()
+
+
+def test_two_sm_kernel_agrees_on_random_shapes():
+    """The cta_group::2 kernel (CTA pairs, 256-row tiles) gives the integers of the plain-conversion
+    tensor-core kernel on ragged shapes, with and without split-K, for both weight layouts."""
+    from fxpr_vllm import _native as nat
+
+    g = torch.Generator().manual_seed(77)
+    for case in range(24):
+        M = int(torch.randint(129, 900, (1,), generator=g))
+        N = 8 * int(torch.randint(16, 130, (1,), generator=g))
+        K = 8 * int(torch.randint(8, 300, (1,), generator=g))
+        kt = (64, 128)[case % 2]
+        split = (1, 2, 3, 5)[case % 4]
+        int_bits = (64, 32)[(case // 2) % 2]
+        dtype = (torch.bfloat16, torch.float16)[(case // 4) % 2]
+        flag = nat.GEMM_PAIR | (nat.GEMM_TILE_N128 if case % 3 == 0 else 0)
+        a = _rand((M, K), dtype, 3000 + case).cuda()
+        b = _rand((K, N), dtype, 4000 + case, 0.05).cuda()
+        if case % 5 == 0:
+            a[M // 2, : min(64, K)] = 3.0e4
+        bb = b if case % 2 else b.t().contiguous().t()
+        bias = _rand((N,), dtype, 5000 + case).cuda() if case % 2 else None
+        with L.overrides(gemm_k_tile=kt, gemm_split_k=split, gemm_flags=flag):
+            got = torch.ops.fxpr.gemm_fxp_int(a, bb, int_bits, 16)
+            got_c = _gemm(a, bb, bias, int_bits, 16)
+        with L.overrides(gemm_k_tile=kt, gemm_split_k=1, gemm_flags=nat.GEMM_FORCE_EXACT_TC):
+            exp = torch.ops.fxpr.gemm_fxp_int(a, bb, int_bits, 16)
+            exp_c = _gemm(a, bb, bias, int_bits, 16)
+        assert torch.equal(got, exp), (case, M, N, K, kt, split, int_bits, dtype)
+        assert torch.equal(got_c.view(torch.int16), exp_c.view(torch.int16)), case
     L.check_device_status()

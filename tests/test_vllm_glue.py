@@ -220,8 +220,13 @@ def test_attention_impl_forward_equals_the_op_and_copies_back_other_dtypes():
 
 
 @pytest.mark.gpu
-def test_linear_method_process_weights_and_apply_equal_the_gemm_op():
+def test_linear_method_process_weights_and_apply_equal_the_gemm_op(monkeypatch):
     import fxpr_vllm  # noqa: F401
+    import vllm.model_executor.parameter as vparam
+
+    # vLLM's weight parameters ask the (uninitialised) TP group for rank and size
+    monkeypatch.setattr(vparam, "get_tensor_model_parallel_rank", lambda: 0)
+    monkeypatch.setattr(vparam, "get_tensor_model_parallel_world_size", lambda: 1)
     from fxpr_vllm.config import get_runtime_config
     from fxpr_vllm.quantisation_config import (FixedPointConfig, FixedPointEmbeddingMethod,
                                                FixedPointLinearMethod)

@@ -388,7 +388,7 @@ static constexpr int64_t kMaxSplitTiles = kLockBytes / 4;
 static int64_t tc_lock_bytes(int64_t, int64_t) { return kLockBytes; }
 
 int64_t gemm_tc_scratch_bytes(int64_t M, int64_t N, int int_bits, int split_k) {
-  const int64_t rows = ((M + kBM - 1) / kBM) * kBM;
+  const int64_t rows = ((M + 255) / 256) * 256;       // the two-SM kernel works on 256-row pair tiles
   const int64_t cols = ((N + 255) / 256) * 256;
   const int64_t planes = (int64_t)(split_k < 1 ? 1 : split_k) * rows * cols * (int_bits == 64 ? 8 : 4);
   return tc_lock_bytes(M, N) + ((planes + 255) / 256) * 256;
@@ -422,8 +422,8 @@ int gemm_tc_n256(const GemmArgs& g, TcParams& p, const CUtensorMap& ma, const CU
 int gemm_tc_skinny(const GemmArgs& g, TcParams& p, const CUtensorMap& mw, cudaStream_t s);
 int gemm_tc_fast(const GemmArgs& g, TcParams& p, const CUtensorMap& ma, const CUtensorMap& mb,
                  cudaStream_t s);
-bool gemm_tc_lean_supported(const GemmArgs& g, int split_k);
-int gemm_tc_lean(const GemmArgs& g, TcParams& p, const CUtensorMap& ma, const CUtensorMap& mb,
+bool gemm_tc_pair_supported(const GemmArgs& g, int split_k);
+int gemm_tc_pair(const GemmArgs& g, TcParams& p, const CUtensorMap& ma, const CUtensorMap& mb,
                  int bn, cudaStream_t s);
 
 int gemm_tc(const GemmArgs& g, cudaStream_t s) {
@@ -446,7 +446,6 @@ int gemm_tc(const GemmArgs& g, cudaStream_t s) {
   }
 
   TcParams p;
-  p.dbg = 0;
   p.bias = g.bias; p.c = g.c; p.c_int = g.c_int; p.partials = g.partials;
   p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K; p.c_sm = g.c_sm;
   p.k_tile = g.k_tile; p.int_bits = g.int_bits;
@@ -473,11 +472,10 @@ int gemm_tc(const GemmArgs& g, cudaStream_t s) {
   // 128 x 256 tiles: measured +6 % at k_tile 128 (two 64-deep stages per accumulator) and -12 %
   // at k_tile 64 (one MMA group per hand-off with only two accumulators in TMEM), same bits;
   // so they are the default for k_tile 128 only.  The flags force either shape.
-  if ((g.flags & FXPR_GEMM_LEAN) && !(g.flags & FXPR_GEMM_FORCE_EXACT_TC) && gemm_tc_lean_supported(g, p.split_k)) {
+  if ((g.flags & FXPR_GEMM_PAIR) && !(g.flags & FXPR_GEMM_FORCE_EXACT_TC) && gemm_tc_pair_supported(g, p.split_k)) {
     int bn = (g.N >= 256) ? 256 : 128;
     if (g.flags & FXPR_GEMM_TILE_N128) bn = 128;
-    if ((g.flags & FXPR_GEMM_TILE_N256) && g.N >= 256) bn = 256;
-    return gemm_tc_lean(g, p, ma, mb, bn, s);
+    return gemm_tc_pair(g, p, ma, mb, bn, s);
   }
   const bool want_n256 = (g.flags & FXPR_GEMM_TILE_N256) || (g.k_tile == 128 && !(g.flags & FXPR_GEMM_TILE_N128));
   if (want_n256 && !(g.flags & FXPR_GEMM_FORCE_EXACT_TC) && gemm_tc_n256_supported(g, p.split_k))

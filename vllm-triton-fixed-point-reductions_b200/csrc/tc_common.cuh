@@ -148,7 +148,7 @@ struct TcParams {
   void* acc_scratch; int32_t* locks; int32_t* status;
   int M, N, K; int64_t c_sm;
   int k_tile, split_k, int_bits; float scale, inv_scale;
-  int tiles_m, tiles_n; uint32_t idesc; int b_kmajor; int c_vec_ok; int dbg; int flush_every;
+  int tiles_m, tiles_n; uint32_t idesc; int b_kmajor; int c_vec_ok;
 };
 
 template <int BN, int STAGES>

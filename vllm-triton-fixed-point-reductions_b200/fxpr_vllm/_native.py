@@ -46,7 +46,7 @@ GEMM_FORCE_PORTABLE = 1
 GEMM_FORCE_EXACT_TC = 2
 GEMM_NO_SKINNY = 8
 GEMM_NO_CLUSTER = 16
-GEMM_LEAN = 256
+GEMM_PAIR = 512
 GEMM_TILE_N256 = 64
 GEMM_TILE_N128 = 128
 ATTN_CAUSAL = 1
