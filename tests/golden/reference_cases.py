@@ -42,6 +42,10 @@ def attention_cases():
         ([300, 77, 1024], [1, 1, 1], 32, 8, 128, 16, torch.bfloat16, 64, 4),
         ([130, 257], [130, 257], 8, 2, 64, 16, torch.float16, 32, 1),
         ([200, 64], [5, 64], 4, 2, 32, 16, torch.bfloat16, 32, 2),
+        # the benchmark geometry (bf16, 32 query / 8 KV heads, head size 128, 16-token pages):
+        ([80, 33], [80, 33], 32, 8, 128, 16, torch.bfloat16, 64, 1),        # prefill
+        ([4500, 700, 64], [1, 1, 1], 32, 8, 128, 16, torch.bfloat16, 64, 8),  # long decode, 8 KV splits
+        ([150], [150], 32, 8, 128, 16, torch.bfloat16, 64, 2),             # prefill through the split kernels
     ]
     for i, (sl, ql, hq, hkv, d, page, dt, bits, splits) in enumerate(specs):
         g = _g(300 + i)
@@ -70,3 +74,9 @@ def rms_cases():
         w = (1 + 0.1 * torch.randn(hidden, generator=g)).to(dt)
         out.append((f"rms_{i}", x, r, w))
     return out
+
+
+# Rows / heads of the integer accumulators that the fixture keeps (the full tensors would be
+# several MB): the GEMM's first rows, and for attention these heads of every token.
+GEMM_INT_ROWS = 32
+ATTN_INT_HEADS = (0, 5, 31)
