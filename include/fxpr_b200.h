@@ -50,6 +50,7 @@ extern "C" {
 #define FXPR_ATTN_CAUSAL         1
 #define FXPR_ATTN_FORCE_PORTABLE 2  /* route to the CUDA-core kernel (sequential partials) */
 #define FXPR_ATTN_EXACT_CONVERT  4  /* tensor-core route with cvt.rni.sat conversions only (tests: same bits as the default) */
+#define FXPR_ATTN_NO_TCGEN05     8  /* prefill on the mma.sync kernel instead of the tcgen05 one (tests: same bits) */
 
 int fxpr_version(void);
 const char* fxpr_status_string(int status);

@@ -65,7 +65,6 @@ extern "C" int fxpr_attention(const void* q, const void* k_cache, const void* v_
                               double logit_softcap, int window, int int_bits, int frac_bits,
                               int num_splits, void* scratch, int64_t scratch_bytes,
                               int32_t* status_word, void* stream) {
-  (void)status_word;  // no kernel on this path spins on a flag; reserved
   if (total_q_tokens < 0 || num_reqs < 0 || num_heads <= 0 || num_kv_heads <= 0 || head_dim <= 0 ||
       page_size <= 0 || window < 0)
     return FXPR_ERR_BAD_ARG;
@@ -97,8 +96,13 @@ extern "C" int fxpr_attention(const void* q, const void* k_cache, const void* v_
 
   // The tensor-core route merges its splits through distributed shared memory and needs
   // no scratch; only the CUDA-core route uses the caller's buffer.
-  if (!(flags & FXPR_ATTN_FORCE_PORTABLE) && attention_mma_supported(p, dtype))
-    return attention_mma(p, dtype, max_query_len, (flags & FXPR_ATTN_EXACT_CONVERT) != 0, s);
+  if (!(flags & FXPR_ATTN_FORCE_PORTABLE) && attention_mma_supported(p, dtype)) {
+    const bool exact = (flags & FXPR_ATTN_EXACT_CONVERT) != 0;
+    // prefill blocks without a KV split: tcgen05 kernel (same bits as the mma.sync kernel)
+    if (!(flags & FXPR_ATTN_NO_TCGEN05) && attention_tc_supported(p, dtype, max_query_len, exact))
+      return attention_tc(p, dtype, max_query_len, status_word, s);
+    return attention_mma(p, dtype, max_query_len, exact, s);
+  }
   if (num_splits > 1) {
     const AttnScratchLayout l = attn_scratch_layout(total_q_tokens, num_heads, head_dim, num_splits);
     if (!scratch || scratch_bytes < l.total) return FXPR_ERR_SCRATCH;

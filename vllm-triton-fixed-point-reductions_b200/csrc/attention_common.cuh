@@ -42,5 +42,8 @@ inline AttnScratchLayout attn_scratch_layout(int64_t total_q, int heads, int hea
 int attention_portable(const AttnParams& p, int dtype, cudaStream_t s);
 int attention_mma(const AttnParams& p, int dtype, int max_query_len, bool force_exact, cudaStream_t s);
 bool attention_mma_supported(const AttnParams& p, int dtype);
+// tcgen05 / TMEM / TMA prefill kernel (attention_tc.cu)
+bool attention_tc_supported(const AttnParams& p, int dtype, int max_query_len, bool force_exact);
+int attention_tc(const AttnParams& p, int dtype, int max_query_len, int32_t* status, cudaStream_t s);
 
 }  // namespace fxpr

@@ -52,6 +52,7 @@ GEMM_TILE_N128 = 128
 ATTN_CAUSAL = 1
 ATTN_FORCE_PORTABLE = 2
 ATTN_EXACT_CONVERT = 4
+ATTN_NO_TCGEN05 = 8
 
 _c = ctypes
 _vp, _i, _i64, _f, _d = _c.c_void_p, _c.c_int, _c.c_int64, _c.c_float, _c.c_double
