@@ -232,3 +232,44 @@ def test_tensor_core_route_feature_flags_close_to_oracle(dtype, kwargs, splits):
     frac = kw.get("frac_bits", 16)
     tol = (2.0 ** -7 if dtype == torch.bfloat16 else 2.0 ** -9) * 2 + 8 * 2.0 ** -frac
     assert (got.float().cpu() - exp).abs().max().item() <= tol * max(1.0, float(exp.abs().max()))
+
+
+@pytest.mark.parametrize("case", [
+    # (seq_lens, q_lens, q heads, kv heads, page, dtype, int_bits, extra arguments)
+    ([80, 33], [80, 33], 32, 8, 16, torch.bfloat16, 64, {}),
+    ([200, 64, 17], [5, 64, 17], 32, 8, 16, torch.bfloat16, 64, {}),          # chunked prefill + short rows
+    ([1000, 333], [1000, 333], 32, 8, 16, torch.bfloat16, 32, {}),
+    ([500, 129], [100, 129], 8, 8, 32, torch.float16, 64, {}),                # no GQA, 32-token pages
+    ([300, 257], [300, 200], 16, 2, 16, torch.bfloat16, 64, dict(softcap=30.0)),
+    ([300, 257], [300, 200], 32, 8, 16, torch.bfloat16, 64, dict(window=100)),
+    ([300, 257], [300, 200], 32, 8, 16, torch.bfloat16, 64, dict(causal=False)),
+    ([300, 257], [300, 200], 32, 8, 16, torch.bfloat16, 64, dict(alibi=True)),
+    ([2100], [2100], 32, 8, 16, torch.bfloat16, 64, {}),
+    ([700, 90], [700, 90], 32, 8, 64, torch.bfloat16, 64, {}),                # 64-token pages: one box per tile
+    ([700, 90], [300, 90], 32, 8, 128, torch.float16, 32, {}),
+])
+def test_tcgen05_prefill_kernel_equals_mma_sync_kernel(case):
+    """The tcgen05 / tensor-memory prefill kernel against the mma.sync kernel it replaces: a
+    tcgen05.mma chain of 16-deep steps gives the same fp32 bits as the mma.sync.m16n8k16 chain,
+    every other step is the same instruction, so the outputs are equal bit for bit -- which is
+    also what keeps a prefill row equal to the decode step of the same token."""
+    from fxpr_vllm import _native as nat
+    from fxpr_vllm import synthetic as syn
+
+    sls, qls, hq, hkv, page, dtype, int_bits, kw = case
+    kw = dict(kw)
+    q, kv, qsl, sl, bt = syn.paged_attention_inputs(sls, qls, q_heads=hq, kv_heads=hkv, head_dim=128, page=page,
+                                                    dtype=dtype, seed=100 + len(sls) + hq)
+    alibi = None
+    if kw.pop("alibi", False):
+        alibi = torch.arange(1, hq + 1, device="cuda", dtype=torch.float32) * 0.01 * orc.RCP_LN2
+    outs = []
+    for flags in (0, nat.ATTN_NO_TCGEN05):
+        o = torch.full_like(q, float("nan"))
+        with L.overrides(attn_flags=flags):
+            torch.ops.fxpr.unified_attention_fxp(q, kv, o, qsl, sl, bt, max(qls), alibi, kw.get("causal", True), None,
+                                                 int_bits, 16, kw.get("softcap", 0.0), kw.get("window", 0), 1)
+        outs.append(o)
+    L.check_device_status()
+    assert not outs[0].isnan().any()
+    assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))

@@ -15,14 +15,15 @@
 // a decode step" (the decode kernel stays on mma.sync) and is what the tests assert.
 //
 // One CTA = 128 query rows of one KV head: a row is a (token, query head of the GQA group)
-// pair, so a K/V tile is fetched once for the whole group.  10 warps:
+// pair, so a K/V tile is fetched once for the whole group.  18 warps:
 //   warp 0      producer: Q (once) and the K / V tiles of the paged cache by TMA, one box of
 //               16 keys x 64 head dims per page and half head (a 16-key group never straddles
 //               a page: page sizes are multiples of 16), 128-byte swizzle, 4-stage ring
 //   warp 1      tcgen05.mma issuer: S = Q.K^T (128 x 64, 8 steps) into one of two tensor-memory
 //               buffers; P.V (128 x 128, 4 steps, fresh accumulator per tile) into one of two
 //               others, P read from shared memory where the softmax warps put it
-//   warps 2-9   softmax / conversion: thread = one row and half of the columns.  Pass A: row
+//   warps 2-17  softmax / conversion: thread = one row and a quarter of the columns (four
+//               warps per scheduler hide the tensor-memory, MUFU and ALU latencies).  Pass A: row
 //               maxima straight from tensor memory (a row lives in one lane: no shuffles).
 //               Pass B: weights, integer denominator, P -> shared memory (K-major, swizzled,
 //               the A operand of P.V); then the P.V partial of the previous tile is rounded to
@@ -42,8 +43,10 @@ namespace fxpr {
 
 static constexpr int kTcTileN = 64;            // keys per tile (attention.py:32-36)
 static constexpr int kTcRows = 128;            // query rows per CTA = tensor-memory lanes
-static constexpr int kTcSoftWarps = 8;
-static constexpr int kTcThreads = (2 + kTcSoftWarps) * 32;
+static constexpr int kTcColGroups = 4;         // softmax threads per row: each owns 64/4 keys and HD/4 output columns
+static constexpr int kTcSoftWarps = 4 * kTcColGroups;
+static constexpr int kTcFirstSoft = 2;         // warp 0: TMA producer, warp 1: MMA issuer
+static constexpr int kTcThreads = (kTcFirstSoft + kTcSoftWarps) * 32;
 static constexpr int kTcStages = 4;
 
 struct TcAttnShape {
@@ -51,6 +54,8 @@ struct TcAttnShape {
   int tokens_per_block;    // 128 / rows_per_token
   int num_q_blocks;
   int page_size;
+  int group_shift;         // log2 of the keys per TMA box: 6 when pages are multiples of 64 tokens, else 4
+  int page_mask;           // page_size - 1 when the page size is a power of two, else 0
   uint32_t idesc_s, idesc_pv;
 };
 
@@ -86,6 +91,24 @@ template <> __device__ __forceinline__ uint32_t pack2_tc<__half>(float lo, float
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Wait used by the 16 softmax warps: one lane polls and sleeps between probes, so that the
+// waiting warps leave the issue slots to the two single-lane role warps that they wait for.
+__device__ __forceinline__ bool warp_wait_relaxed(uint32_t bar, uint32_t parity, volatile int* abort_flag, int lane) {
+  int ok = 1;
+  if (lane == 0 && !mbar_try_wait(bar, parity)) {
+    const long long t0 = clock64();
+    int spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+      __nanosleep(40);
+      if ((++spins & 63) == 0) {
+        if (*abort_flag) { ok = 0; break; }
+        if (clock64() - t0 > kWaitCycles) { *abort_flag = 1; ok = 0; break; }
+      }
+    }
+  }
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
 template <typename T, int HD>
 __global__ void __launch_bounds__(kTcThreads, 1)
 attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -97,7 +120,10 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   constexpr int kStageBytes = 2 * kKBytes;                 // K then V
   constexpr int kPBytes = kTcRows * kTcTileN * 2;          // 16 KB: 128 rows x 128 B
   constexpr int kBarOffset = kQBytes + kTcStages * kStageBytes + 2 * kPBytes;
-  constexpr int kHalfCols = HD / 2;                        // P.V columns per thread
+  constexpr int CG = kTcColGroups;
+  constexpr int KT = kTcTileN / CG;                        // keys per softmax thread and tile
+  constexpr int kHalfCols = HD / CG;                       // P.V columns per thread
+  static_assert(KT == 16 && kHalfCols == 32, "one 16-column and one 32-column tensor-memory load per tile");
   constexpr uint32_t kColS = 0, kColPV = 128;              // tensor-memory columns: S[2] x 64, PV[2] x 128
 
   extern __shared__ uint8_t smem_raw[];
@@ -112,8 +138,8 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   constexpr int kMisc = 8 * (1 + 2 * kTcStages + 10 + 1);
   volatile uint32_t* tmem_slot = (volatile uint32_t*)(smem_gen + kBarOffset + kMisc);
   volatile int* abort_flag = (volatile int*)(smem_gen + kBarOffset + kMisc + 8);
-  float* rmax_s = (float*)(smem_gen + kBarOffset + kMisc + 16);                 // [2][128]
-  long long* den_s = (long long*)(smem_gen + kBarOffset + kMisc + 16 + 1024);   // [2][128]
+  float* rmax_s = (float*)(smem_gen + kBarOffset + kMisc + 16);                 // [CG][128]
+  long long* den_s = (long long*)(smem_gen + kBarOffset + kMisc + 16 + 2048);   // [CG][128]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -134,6 +160,11 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int t1 = max(t0, (hi_key + kTcTileN - 1) / kTcTileN);
   const int n_tiles = t1 - t0;
 
+  if (threadIdx.x == 32) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
+  }
   if (threadIdx.x == 0) {
     mbar_init(qfull, 1);
     for (int s = 0; s < kTcStages; ++s) { mbar_init(full0 + 8u * s, 1); mbar_init(empty0 + 8u * s, 1); }
@@ -156,41 +187,55 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    // ------------------------------ TMA producer --------------------------------------
+    // ------------------------------ K / V producer (TMA) ------------------------------
+    // One box per 16-token page piece and half head (2 KB).  Measured on a B200: an SM keeps
+    // only ~15 bytes per clock of such pieces in flight, whether they are fetched as TMA
+    // boxes, as 16-byte cp.async copies from two or four warps, or as both at once; that,
+    // not the tensor core or the conversion work, bounds this kernel at 16-token pages
+    // (48 KB per 128 x 64 tile over the two passes).  The boxes of a tile are issued from 16
+    // lanes in one instruction: issued one by one they cost the issuing thread ~80 clocks
+    // each.  Nothing is copied, and the block table is not read, past the end of the
+    // sequence; V rows there are cleared by the MMA warp before P.V.
     const int32_t* bt = p.block_table + (int64_t)req * p.bt_stride;
-    if (lane == 0) {
-      // Q rows: box {64 dims, G heads, 128 / G tokens} -> row = token * G + head.  Tokens past
-      // this request's (they belong to the next one, or lie beyond the tensor: zeros) are
-      // rows whose every key is masked and that are never stored.
-      mbar_expect_tx(qfull, kQBytes);
-      tma_load_3d(q_s, &map_q, qfull, 0, kvh * G, q_start + tok0);
-      tma_load_3d(q_s + kQBytes / 2, &map_q, qfull, 64, kvh * G, q_start + tok0);
-    }
-    __syncwarp();
     int stage = 0; uint32_t phase = 1;
+    // Block-table entries are read 32 at a time (lane L: the 16-key group L of an 8-tile
+    // block), one block ahead of their use, and handed round by shuffle.
+    int page_shift = -1;
+    for (int b = 4; b < 31; ++b) if ((1 << b) == sh.page_size) page_shift = b;
+    auto load_entries = [&](int tb) -> int {
+      const int n = tb * kTcTileN + lane * 16;
+      return (tb < t1 && n < seq_len) ? bt[page_shift >= 0 ? (n >> page_shift) : (n / sh.page_size)] : 0;
+    };
     for (int pass = 0; pass < 2; ++pass) {
-      for (int t = t0; t < t1; ++t) {
-        if (!__all_sync(0xffffffffu, mbar_wait(empty0 + 8u * stage, phase, abort_flag))) goto producer_done;
-        if (lane == 0) {
+      int cur = load_entries(t0);
+      for (int tb = t0; tb < t1; tb += 8) {
+        const int nxt = load_entries(tb + 8);
+        for (int tt = 0; tt < 8 && tb + tt < t1; ++tt) {
+          const int t = tb + tt;
+          if (!__all_sync(0xffffffffu, mbar_wait(empty0 + 8u * stage, phase, abort_flag))) goto producer_done;
           const uint32_t fb = full0 + 8u * stage;
-          const uint32_t ks = stage0 + stage * kStageBytes, vs = ks + kKBytes;
-          // 16-key groups that start inside the sequence (the block table is not read past it)
-          int groups = (seq_len - t * kTcTileN + 15) / 16;
-          groups = groups > 4 ? 4 : groups;
-          mbar_expect_tx(fb, (uint32_t)(groups * 2 * 2048 * (pass ? 2 : 1)));
-          for (int g = 0; g < groups; ++g) {
-            const int n = t * kTcTileN + g * 16;
-            const int blk = bt[n / sh.page_size], slot = n % sh.page_size;
-            tma_load_4d(ks + g * 2048, &map_k, fb, 0, kvh, slot, blk);
-            tma_load_4d(ks + 8192 + g * 2048, &map_k, fb, 64, kvh, slot, blk);
-            if (pass) {
-              tma_load_4d(vs + g * 2048, &map_v, fb, 0, kvh, slot, blk);
-              tma_load_4d(vs + 8192 + g * 2048, &map_v, fb, 64, kvh, slot, blk);
-            }
+          const uint32_t ks = stage0 + stage * kStageBytes;
+          // boxes hold group_keys keys (16, or the whole tile when pages are multiples of 64
+          // tokens); only groups that start inside the sequence are copied
+          // (shifts and masks only: this single warp's loop latency is on the critical path)
+          const int gs = sh.group_shift, gk = 1 << gs;
+          int groups = (seq_len - t * kTcTileN + gk - 1) >> gs;
+          groups = min(groups, kTcTileN >> gs);
+          if (lane == 0) mbar_expect_tx(fb, (uint32_t)((groups << (gs + 8)) << pass));
+          __syncwarp();
+          // lane = group * 4 + {K low half, K high half, V low half, V high half}
+          const int g = (lane >> 2) & 3, sel = lane & 3;
+          const int blk = __shfl_sync(0xffffffffu, cur, tt * 4 + (gs == 4 ? g : 0));
+          if (lane < 16 && g < groups && (pass || sel < 2)) {
+            const int n = t * kTcTileN + (g << gs);
+            const int slot = sh.page_mask ? (n & sh.page_mask) : (n % sh.page_size);
+            const uint32_t dst = ks + (uint32_t)((sel >> 1) * kKBytes + (sel & 1) * 8192 + (g << (gs + 7)));
+            tma_load_4d(dst, (sel >> 1) ? &map_v : &map_k, fb, (sel & 1) * 64, kvh, slot, blk);
           }
+          __syncwarp();
+          if (++stage == kTcStages) { stage = 0; phase ^= 1; }
         }
-        __syncwarp();
-        if (++stage == kTcStages) { stage = 0; phase ^= 1; }
+        cur = nxt;
       }
     }
   producer_done:;
@@ -212,6 +257,15 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
       __syncwarp();
     };
+    if (lane == 0) {
+      // Q rows: box {64 dims, G heads, 128 / G tokens} -> row = token * G + head.  Tokens past
+      // this request's (they belong to the next one, or lie beyond the tensor: zeros) are
+      // rows whose every key is masked and that are never stored.
+      mbar_expect_tx(qfull, kQBytes);
+      tma_load_3d(q_s, &map_q, qfull, 0, kvh * G, q_start + tok0);
+      tma_load_3d(q_s + kQBytes / 2, &map_q, qfull, 64, kvh * G, q_start + tok0);
+    }
+    __syncwarp();
     bool okq = mbar_wait(qfull, 0, abort_flag);
     if (!__all_sync(0xffffffffu, okq)) goto issuer_done;
     {
@@ -282,10 +336,10 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
     }
   issuer_done:;
-  } else {
+  } else if (warp >= kTcFirstSoft) {
     // ------------------------------ softmax / conversion warps ------------------------
     const int quarter = warp & 3;
-    const int half = (warp - 2) >> 2;                        // which half of the columns
+    const int half = (warp - kTcFirstSoft) >> 2;                        // which quarter of the columns
     const int row = quarter * 32 + lane;                     // tensor-memory lane = query row
     const uint32_t lane_sel = (uint32_t)(quarter * 32) << 16;
     const int tok = tok0 + row / G, head = kvh * G + row % G;
@@ -302,28 +356,28 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     auto soft_sync = [&]() -> bool {                         // bounded barrier over these 8 warps
       __syncwarp();
       if (lane == 0) mbar_arrive(soft_bar);
-      const bool done = warp_wait(soft_bar, soft_phase, abort_flag, lane);
+      const bool done = warp_wait_relaxed(soft_bar, soft_phase, abort_flag, lane);
       soft_phase ^= 1;
       return done;
     };
     // scores of this thread's 32 keys of tile t, in log2 space, masked (attention.py:103-121, 249-254)
-    auto load_scores = [&](int it, int t, float (&s)[32]) -> bool {
+    auto load_scores = [&](int it, int t, float (&s)[KT]) -> bool {
       const int sb = it & 1; const uint32_t sph = (it >> 1) & 1;
-      if (!warp_wait(sfull0 + 8u * sb, sph, abort_flag, lane)) return false;
+      if (!warp_wait_relaxed(sfull0 + 8u * sb, sph, abort_flag, lane)) return false;
       tc_fence_after();
-      uint32_t v[32];
-      tmem_ld32(tmem_base + lane_sel + kColS + (uint32_t)(sb * 64 + half * 32), v);
+      uint32_t v[KT];
+      tmem_ld16(tmem_base + lane_sel + kColS + (uint32_t)(sb * 64 + half * KT), v);
       tmem_wait_ld();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(sfree0 + 8u * sb);          // the buffer may take the tile after next
-      const int n0 = t * kTcTileN + half * 32;
-      if (plain_scores && n0 >= kbeg && n0 + 32 <= kend) {
+      const int n0 = t * kTcTileN + half * KT;
+      if (plain_scores && n0 >= kbeg && n0 + KT <= kend) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) s[i] = __fmul_rn(__uint_as_float(v[i]), p.ss_log2);
+        for (int i = 0; i < KT; ++i) s[i] = __fmul_rn(__uint_as_float(v[i]), p.ss_log2);
       } else {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
+        for (int i = 0; i < KT; ++i) {
           const int n = n0 + i;
           float x = __fmul_rn(__uint_as_float(v[i]), p.ss_log2);
           if (p.cap_log2 > 0.0f) x = __fmul_rn(p.cap_log2, tanhf(__fdiv_rn(x, p.cap_log2)));
@@ -338,18 +392,24 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     float rmax = ninf;
     int it = 0;
     for (int t = t0; t < t1 && ok; ++t, ++it) {
-      float s[32];
+      float s[KT];
       if (!load_scores(it, t, s)) { ok = false; break; }
+      // max is exact and order-free: a tree keeps the dependency chain short
 #pragma unroll
-      for (int i = 0; i < 32; ++i) rmax = fmaxf(rmax, s[i]);
+      for (int w = KT / 2; w > 0; w >>= 1)
+#pragma unroll
+        for (int i = 0; i < w; ++i) s[i] = fmaxf(s[i], s[i + w]);
+      rmax = fmaxf(rmax, s[0]);
     }
     rmax_s[half * kTcRows + row] = rmax;
     if (ok && !soft_sync()) ok = false;
-    float gmax = fmaxf(rmax_s[row], rmax_s[kTcRows + row]);
+    float gmax = rmax_s[row];
+#pragma unroll
+    for (int c = 1; c < CG; ++c) gmax = fmaxf(gmax, rmax_s[c * kTcRows + row]);
     if (gmax == ninf) gmax = 0.0f;                           // rows without keys: exp2 gives 0, not NaN
 
     // =============================== pass B ===========================================
-    uint32_t den32 = 0;
+    uint32_t den32 = 0, den32b = 0;                         // two chains: integer adds commute
     uint32_t acc[kHalfCols];
 #pragma unroll
     for (int i = 0; i < kHalfCols; ++i) acc[i] = 0;
@@ -360,23 +420,25 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // round the P.V partial of tile j (this thread's 64 columns) to Q-format and add it
     auto convert_pv = [&](int j) -> bool {
       const int b = j & 1; const uint32_t ph = (j >> 1) & 1;
-      if (!warp_wait(pvfull0 + 8u * b, ph, abort_flag, lane)) return false;
+      if (!warp_wait_relaxed(pvfull0 + 8u * b, ph, abort_flag, lane)) return false;
       tc_fence_after();
       const uint32_t taddr = tmem_base + lane_sel + kColPV + (uint32_t)(b * HD + half * kHalfCols);
-      uint32_t screen = 0;
-#pragma unroll
-      for (int c = 0; c < kHalfCols / 32; ++c) {
+      uint32_t screen = 0, screen_b = 0;
+      {
         uint32_t v[32];
-        tmem_ld32(taddr + c * 32, v);
+        tmem_ld32(taddr, v);
         tmem_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const uint32_t r = __float_as_uint(__fmaf_rn(__uint_as_float(v[i]), p.scale, magic));
-          acc[c * 32 + i] += r;
-          screen |= r ^ kExpBits;
+        for (int i = 0; i < 32; i += 2) {
+          const uint32_t ra = __float_as_uint(__fmaf_rn(__uint_as_float(v[i]), p.scale, magic));
+          const uint32_t rb = __float_as_uint(__fmaf_rn(__uint_as_float(v[i + 1]), p.scale, magic));
+          acc[i] += ra;
+          acc[i + 1] += rb;
+          screen |= ra ^ kExpBits;
+          screen_b |= rb ^ kExpBits;
         }
       }
-      if (__any_sync(0xffffffffu, (screen >> 23) != 0)) {
+      if (__any_sync(0xffffffffu, ((screen | screen_b) >> 23) != 0)) {
         // some partial left the fast range: exact conversion of the offending elements
         if (!corr_used) {
 #pragma unroll 1
@@ -393,14 +455,14 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
     for (int j = 0; j < n_tiles && ok; ++j, ++it) {
       const int t = t0 + j;
-      float s[32];
+      float s[KT];
       if (!load_scores(it, t, s)) { ok = false; break; }
       // weights, integer denominator, P in the io dtype -> shared memory (A operand of P.V):
       // row = 128 bytes of 64 keys, 16-byte chunks XOR-swizzled with the row number
       const int b = j & 1;
       const uint32_t prow = p_s0 + b * kPBytes + (uint32_t)row * 128u;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < KT / 8; ++c) {
         uint32_t pk[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -408,10 +470,10 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           const float w0 = (s0 == ninf) ? 0.0f : ex2_approx_tc(__fsub_rn(s0, gmax));
           const float w1 = (s1 == ninf) ? 0.0f : ex2_approx_tc(__fsub_rn(s1, gmax));
           den32 += __float_as_uint(__fmaf_rn(w0, p.scale, magic));
-          den32 += __float_as_uint(__fmaf_rn(w1, p.scale, magic));
+          den32b += __float_as_uint(__fmaf_rn(w1, p.scale, magic));
           pk[e] = pack2_tc<T>(w0, w1);
         }
-        const uint32_t chunk = (uint32_t)(half * 4 + c);
+        const uint32_t chunk = (uint32_t)(half * (KT / 8) + c);
         const uint32_t addr = prow + ((chunk ^ (uint32_t)(row & 7)) << 4);
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]) : "memory");
       }
@@ -423,12 +485,14 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (ok && n_tiles > 0 && !convert_pv(n_tiles - 1)) ok = false;
 
     // =============================== output ===========================================
-    // 32 weights per tile went through the fast add in this thread
-    const long long den_half = (long long)(int32_t)(den32 - 32u * (uint32_t)n_tiles * kMagicBits);
+    // KT weights per tile went through the fast add in this thread
+    const long long den_half = (long long)(int32_t)(den32 + den32b - (uint32_t)KT * (uint32_t)n_tiles * kMagicBits);
     den_s[half * kTcRows + row] = den_half;
     if (ok && !soft_sync()) ok = false;
     if (ok && valid) {
-      const long long dsum = den_s[row] + den_s[kTcRows + row];
+      long long dsum = den_s[row];
+#pragma unroll
+      for (int c = 1; c < CG; ++c) dsum += den_s[c * kTcRows + row];
       const float dn = fmaxf(fixed_to_float<long long>(wrap_to_bits(dsum, p.int_bits), p.inv_scale), 1.0e-6f);
       T* op = (T*)p.o + (int64_t)(q_start + tok) * p.o_st + (int64_t)head * p.o_sh + half * kHalfCols;
       const uint32_t bias_bits = (uint32_t)n_tiles * kMagicBits;
@@ -439,14 +503,15 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         for (int i = 0; i < 8; ++i) {
           const int c = g8 * 8 + i;
           uint32_t raw = acc[c] - bias_bits;
-          long long tot;
+          float num;
           if (corr_used) {
             raw -= corr_raw[c + zero];
-            tot = (long long)(int32_t)raw + corr_q[c + zero];
+            const long long tot = (long long)(int32_t)raw + corr_q[c + zero];
+            num = fixed_to_float<long long>(wrap_to_bits(tot, p.int_bits), p.inv_scale);
           } else {
-            tot = (long long)(int32_t)raw;
+            // the sum fits 32 bits: the same value through the cheaper 32-bit conversion
+            num = fixed_to_float<int>((int)raw, p.inv_scale);
           }
-          const float num = fixed_to_float<long long>(wrap_to_bits(tot, p.int_bits), p.inv_scale);
           out[i] = from_f32<T>(__fdiv_rn(num, dn));
         }
         *reinterpret_cast<uint4*>(op + g8 * 8) = *reinterpret_cast<const uint4*>(out);
@@ -521,6 +586,8 @@ int attention_tc(const AttnParams& p, int dtype, int max_query_len, int32_t* sta
   sh.tokens_per_block = kTcRows / G;
   sh.num_q_blocks = (max_query_len + sh.tokens_per_block - 1) / sh.tokens_per_block;
   sh.page_size = p.page_size;
+  sh.group_shift = (p.page_size % 64 == 0) ? 6 : 4;
+  sh.page_mask = (p.page_size & (p.page_size - 1)) == 0 ? p.page_size - 1 : 0;
   const int fmt = dtype == FXPR_BF16 ? 1 : 0;
   sh.idesc_s = make_idesc(fmt, 0, kTcTileN, kTcRows);
   sh.idesc_pv = make_idesc(fmt, 1, p.head_dim, kTcRows);
@@ -546,7 +613,7 @@ int attention_tc(const AttnParams& p, int dtype, int max_query_len, int32_t* sta
     cuuint64_t dims[4] = {(cuuint64_t)p.head_dim, (cuuint64_t)p.num_kv_heads, (cuuint64_t)p.page_size,
                           (cuuint64_t)1 << 31};
     cuuint64_t strides[3] = {(cuuint64_t)p.kv_shead * 2, (cuuint64_t)p.kv_sslot * 2, (cuuint64_t)p.kv_sblock * 2};
-    cuuint32_t box[4] = {64, 1, 16, 1};
+    cuuint32_t box[4] = {64, 1, (cuuint32_t)(1 << sh.group_shift), 1};
     cuuint32_t es[4] = {1, 1, 1, 1};
     if (fn(which ? &mv : &mk, dt, 4, const_cast<void*>(which ? p.v : p.k), dims, strides, box, es,
            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -557,7 +624,7 @@ int attention_tc(const AttnParams& p, int dtype, int max_query_len, int32_t* sta
   }
 
   constexpr int kSmem = kTcRows * 128 * 2 + kTcStages * 2 * kTcTileN * 128 * 2 + 2 * kTcRows * kTcTileN * 2 +
-                        8 * (1 + 2 * kTcStages + 10 + 1) + 16 + 1024 + 2048 + 1024;
+                        8 * (1 + 2 * kTcStages + 10 + 1) + 16 + 2048 + 4096 + 1024;
   dim3 grid((unsigned)(sh.num_q_blocks * p.num_kv_heads), (unsigned)p.num_reqs, 1);
 #define FXPR_TC_ATTN(TT)                                                                              \
   do {                                                                                                \
