@@ -88,6 +88,22 @@ int fxpr_rms_norm(const void* x, void* residual, const void* weight, void* y,
                   int frac_bits, void* stream);
 
 /*
+ * The step after a tensor-parallel row-parallel GEMM in one kernel: acc is the
+ * all-reduced integer accumulator tensor [rows, hidden] (int{int_bits}, Q(gemm_frac_bits),
+ * as fxpr_gemm's c_int), and the kernel does what fxpr_gemm_epilogue_from_int followed by
+ * fxpr_rms_norm with a residual do, with the same roundings in the same order:
+ * x = T(fp32(acc) * 2^-gemm_frac_bits + bias), residual <- T(x + residual) in place,
+ * y = RMSNorm(residual) with the integer sum of squares (Q(frac_bits), int64).
+ * bias may be NULL.  Rows longer than 16384 elements return FXPR_ERR_UNSUPPORTED (use
+ * the two calls).  No counterpart in the reference (its plugin leaves the reduce to
+ * vLLM's float all-reduce, vllm/model_executor/layers/linear.py).
+ */
+int fxpr_rms_norm_from_int(const void* acc, int int_bits, const void* bias,
+                           void* residual, const void* weight, void* y, int dtype,
+                           int64_t rows, int64_t hidden, float eps,
+                           int gemm_frac_bits, int frac_bits, void* stream);
+
+/*
  * Row-wise log-softmax of a contiguous [rows, cols] matrix into fp32:
  * y = (x - max) - log(sum_int64(Q(exp(x - max)))).  x_dtype in
  * {FXPR_F16, FXPR_BF16, FXPR_F32}.  No counterpart in the reference (the

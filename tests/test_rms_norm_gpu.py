@@ -93,3 +93,25 @@ def test_errors():
     with pytest.raises(ValueError):
         torch.ops.fxpr.rms_norm_fxp_residual(x, torch.randn(2, 4, device="cuda"),
                                              torch.ones(8, device="cuda"), 1e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("int_bits", [32, 64])
+@pytest.mark.parametrize("use_bias", [False, True])
+def test_from_int_kernel_equals_epilogue_then_residual_norm(dtype, int_bits, use_bias):
+    """``rms_norm_fxp_from_int`` (conversion of the all-reduced integer accumulators + bias +
+    residual add + RMSNorm in one kernel, the step after a tensor-parallel row-parallel GEMM)
+    gives the bits of ``gemm_fxp_epilogue`` followed by ``rms_norm_fxp_residual``."""
+    g = torch.Generator().manual_seed(7)
+    rows, hidden = 37, 4096
+    idt = torch.int32 if int_bits == 32 else torch.int64
+    acc = (torch.randn(rows, hidden, generator=g) * 3 * 65536).to(idt).cuda()
+    res = torch.randn(rows, hidden, generator=g).to(dtype).cuda()
+    w = (1 + 0.1 * torch.randn(hidden, generator=g)).to(dtype).cuda()
+    bias = torch.randn(hidden, generator=g).to(dtype).cuda() if use_bias else None
+    r1, r2 = res.clone(), res.clone()
+    x = torch.ops.fxpr.gemm_fxp_epilogue(acc, bias, dtype, 16)
+    want = torch.ops.fxpr.rms_norm_fxp_residual(x, r1, w, 1e-6)
+    got = torch.ops.fxpr.rms_norm_fxp_from_int(acc, r2, w, bias, 1e-6, 16)
+    assert torch.equal(got.view(torch.uint8), want.view(torch.uint8))
+    assert torch.equal(r1.view(torch.uint8), r2.view(torch.uint8))

@@ -36,8 +36,11 @@ def _worker(rank: int, world: int, port: int, int_bits: int, out_dir: str) -> No
         ks = K // world
         out = tp.row_parallel_gemm(
             a[:, rank * ks:(rank + 1) * ks], b[rank * ks:(rank + 1) * ks], bias, int_bits, 16,
-            int_gemm=lambda x, w, ib, fb: orc.gemm_fxp(x, w, None, ib, fb, k_tile=k_tile, return_int=True),
-            epilogue=lambda acc, bs, dt, fb: orc.gemm_epilogue(orc._wrap_to_bits(acc, int_bits), bs, dt, fb))
+            # accumulators in the width the GPU op returns (int16 is widened for the all-reduce)
+            int_gemm=lambda x, w, ib, fb: orc._wrap_to_bits(
+                orc.gemm_fxp(x, w, None, ib, fb, k_tile=k_tile, return_int=True), ib).to(
+                    {16: torch.int16, 32: torch.int32, 64: torch.int64}[ib]),
+            epilogue=lambda acc, bs, dt, fb: orc.gemm_epilogue(orc._wrap_to_bits(acc.to(torch.int64), int_bits), bs, dt, fb))
         full = orc.gemm_fxp(a, b, bias, int_bits, 16, k_tile=k_tile)
         assert torch.equal(out, full), f"rank {rank}: sharded result differs from the unsharded one"
         gathered = [torch.empty_like(out) for _ in range(world)]
@@ -48,7 +51,7 @@ def _worker(rank: int, world: int, port: int, int_bits: int, out_dir: str) -> No
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,int_bits", [(2, 64), (4, 64), (2, 32)])
+@pytest.mark.parametrize("world,int_bits", [(2, 64), (4, 64), (2, 32), (2, 16)])
 def test_row_parallel_integer_allreduce_matches_unsharded(world, int_bits, tmp_path):
     port = 29500 + (os.getpid() % 2000) + world
     mp.spawn(_worker, args=(world, port, int_bits, str(tmp_path)), nprocs=world, join=True)

@@ -44,6 +44,8 @@ _lib.define(
 )
 # additions
 _lib.define("log_softmax_fxp(Tensor x, int fxp_frac_bits) -> Tensor")
+_lib.define("rms_norm_fxp_from_int(Tensor acc, Tensor(a!) residual, Tensor weight, Tensor? bias, float eps, "
+            "int gemm_frac_bits) -> Tensor")
 _lib.define("gemm_fxp_int(Tensor a, Tensor b, int fxp_int_bits, int fxp_frac_bits) -> Tensor")
 _lib.define(
     "gemm_fxp_epilogue(Tensor c_int, Tensor? bias, ScalarType out_dtype, "
@@ -218,6 +220,35 @@ def _rms_norm_launch(x, w, residual, eps):
     if residual is not None and r_storage.data_ptr() != residual.data_ptr():
         residual.copy_(r_storage.view_as(residual))
     return y_2d.view_as(x)
+
+
+def rms_norm_fxp_from_int_run(acc, residual, w, bias, eps, gemm_frac_bits):
+    """Integer accumulators of a row-parallel GEMM (after the cross-rank integer sum) ->
+    GEMM epilogue + residual add + RMSNorm in one kernel.  Same bits as
+    ``gemm_fxp_epilogue`` followed by ``rms_norm_fxp_residual``."""
+    if acc.dtype not in _INT_BITS:
+        raise TypeError(f"rms_norm_fxp_from_int: acc must be an integer tensor, got {acc.dtype}")
+    if not (acc.is_cuda and residual.is_cuda and w.is_cuda):
+        raise RuntimeError("rms_norm_fxp_from_int: tensors must be CUDA")
+    if residual.dtype not in _IO_DTYPES or w.dtype != residual.dtype:
+        raise TypeError("rms_norm_fxp_from_int: residual and weight must share one io dtype")
+    if acc.shape != residual.shape or not (acc.is_contiguous() and residual.is_contiguous()):
+        raise ValueError("rms_norm_fxp_from_int: acc and residual must be contiguous and of one shape")
+    hidden = residual.shape[-1]
+    rows = residual.numel() // hidden if hidden else 0
+    y = torch.empty_like(residual)
+    if rows and hidden:
+        if hidden * 4 > 64 * 1024:
+            x = gemm_fxp_epilogue_run(acc.reshape(rows, hidden), bias, residual.dtype, gemm_frac_bits)
+            return _rms_norm_launch(x.view_as(residual), w, residual, eps)
+        b = None if bias is None else bias.to(residual.dtype).contiguous()
+        with _on_device(acc):
+            st = nat.load().fxpr_rms_norm_from_int(
+                acc.data_ptr(), _INT_BITS[acc.dtype], nat.ptr(b), residual.data_ptr(), w.contiguous().data_ptr(),
+                y.data_ptr(), nat.DTYPE_CODE[residual.dtype], rows, hidden, float(eps), int(gemm_frac_bits),
+                get_runtime_config().fxp_frac_bits, nat.stream_ptr(acc.device))
+        nat.check(st, "rms_norm_fxp_from_int")
+    return y
 
 
 def rms_norm_fxp_run(x, w, eps):
@@ -486,8 +517,14 @@ def pick_num_splits(requested, num_requests, num_q_blocks, num_heads, num_kv_til
 def _tensor_core_route(q, kv_cache, num_heads, num_kv_heads, head_dim, page_size) -> bool:
     """Mirror of the C side's routing rule (dtype / geometry only, never batch)."""
     g = num_heads // num_kv_heads
-    return (q.dtype in (torch.float16, torch.bfloat16) and head_dim in (64, 128)
-            and page_size % 16 == 0 and g in (1, 2, 4, 8, 16) and not _ovr.attn_portable)
+    if not (q.dtype in (torch.float16, torch.bfloat16) and head_dim in (64, 128)
+            and page_size % 16 == 0 and g in (1, 2, 4, 8, 16) and not _ovr.attn_portable):
+        return False
+    # 16-byte copies: row starts must be 16-byte aligned
+    strides = (q.stride(0), q.stride(1), kv_cache.stride(0), kv_cache.stride(2), kv_cache.stride(3))
+    if any(st % 8 for st in strides):
+        return False
+    return (q.data_ptr() | kv_cache.data_ptr() | kv_cache.select(1, 1).data_ptr()) % 16 == 0
 
 
 def pick_num_splits_b200(requested, num_requests, max_query_len, num_heads, num_kv_heads,
@@ -549,7 +586,8 @@ def unified_attention_fxp_run(q, kv_cache, o, query_start_loc, seq_lens, block_t
     num_q_blocks = max(1, -(-max(1, int(max_query_len)) // block_m))
     max_kv_blocks = block_table.shape[1] if block_table.dim() == 2 else 0
     num_kv_tiles = -(-max(1, max_kv_blocks * page_size) // block_n)
-    if _tensor_core_route(q, kv_cache, num_heads, num_kv_heads, head_dim, page_size):
+    tensor_core = _tensor_core_route(q, kv_cache, num_heads, num_kv_heads, head_dim, page_size)
+    if tensor_core:
         splits = pick_num_splits_b200(int(num_kv_splits), num_requests, int(max_query_len),
                                       num_heads, num_kv_heads, max(1, max_kv_blocks * page_size),
                                       _sm_count(q.device))
@@ -560,7 +598,9 @@ def unified_attention_fxp_run(q, kv_cache, o, query_start_loc, seq_lens, block_t
     lib = nat.load()
     scratch = None
     scratch_bytes = 0
-    if splits > 1:
+    if splits > 1 and not tensor_core:
+        # only the CUDA-core route keeps per-split maxima, integer totals and arrival counters
+        # in scratch; the tensor-core kernels merge their splits inside a thread-block cluster
         scratch_bytes = lib.fxpr_attention_scratch_bytes(q.shape[0], num_heads, head_dim,
                                                          fxp_int_bits, splits)
         scratch = torch.empty(scratch_bytes, device=q.device, dtype=torch.uint8)
@@ -583,7 +623,8 @@ def unified_attention_fxp_run(q, kv_cache, o, query_start_loc, seq_lens, block_t
             head_dim, page_size, q.stride(0), q.stride(1), o.stride(0), o.stride(1),
             kv_cache.stride(0), kv_cache.stride(2), kv_cache.stride(3), bt_stride,
             int(max_query_len), flags, ss, float(logit_softcap), int(window_size),
-            fxp_int_bits, fxp_frac_bits, splits, nat.ptr(scratch), scratch_bytes, None,
+            fxp_int_bits, fxp_frac_bits, splits, nat.ptr(scratch), scratch_bytes,
+            _status_word(q.device).data_ptr(),
             nat.stream_ptr(q.device))
     nat.check(st, "unified_attention_fxp")
 
@@ -610,6 +651,11 @@ def _fixed_to_float_cuda(x, float_bits, fxp_frac_bits):
 @torch.library.impl("fxpr::rms_norm_fxp", "CUDA", lib=_lib)
 def _rms_norm_fxp_cuda(x, weight, eps):
     return rms_norm_fxp_run(x, weight, float(eps))
+
+
+@torch.library.impl("fxpr::rms_norm_fxp_from_int", "CUDA", lib=_lib)
+def _rms_norm_fxp_from_int_cuda(acc, residual, weight, bias, eps, gemm_frac_bits):
+    return rms_norm_fxp_from_int_run(acc, residual, weight, bias, float(eps), int(gemm_frac_bits))
 
 
 @torch.library.impl("fxpr::rms_norm_fxp_residual", "CUDA", lib=_lib)

@@ -65,6 +65,7 @@ SIGNATURES = {
     "fxpr_float_to_fixed": (_i, [_vp, _i, _vp, _i, _i, _i64, _vp]),
     "fxpr_fixed_to_float": (_i, [_vp, _i, _vp, _i, _i, _i64, _vp]),
     "fxpr_rms_norm": (_i, [_vp, _vp, _vp, _vp, _i, _i64, _i64, _f, _i, _vp]),
+    "fxpr_rms_norm_from_int": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _i, _i64, _i64, _f, _i, _i, _vp]),
     "fxpr_log_softmax": (_i, [_vp, _i, _vp, _i64, _i64, _i, _vp]),
     "fxpr_rope_kv_write": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _i64, _i, _i, _i, _i,
                                 _i64, _i64, _i64, _i64, _vp]),

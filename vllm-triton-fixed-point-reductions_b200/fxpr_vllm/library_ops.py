@@ -46,6 +46,11 @@ def _(x, residual, weight_fp32, eps):
     return torch.empty_like(x)
 
 
+@_fake("rms_norm_fxp_from_int")
+def _(acc, residual, weight, bias, eps, gemm_frac_bits):
+    return torch.empty_like(residual)
+
+
 @_fake("gemm_fxp")
 def _(a, b, bias, fxp_int_bits, fxp_frac_bits):
     return a.new_empty((a.shape[0], b.shape[1]))
@@ -77,6 +82,7 @@ def _(c_int, bias, out_dtype, fxp_frac_bits):
 gemm_fxp = torch.ops.fxpr.gemm_fxp
 rms_norm_fxp = torch.ops.fxpr.rms_norm_fxp
 rms_norm_fxp_residual = torch.ops.fxpr.rms_norm_fxp_residual
+rms_norm_fxp_from_int = torch.ops.fxpr.rms_norm_fxp_from_int
 float_to_fixed = torch.ops.fxpr.float_to_fixed
 fixed_to_float = torch.ops.fxpr.fixed_to_float
 unified_attention_fxp = torch.ops.fxpr.unified_attention_fxp

@@ -171,14 +171,18 @@ class LlamaDecoder:
         cache[blk, 0, slot] = k
         cache[blk, 1, slot] = v
 
-    def _row_parallel(self, acts, weights):
+    def _row_parallel_norm(self, acts, weights, residual, norm_w):
+        """Row-parallel GEMM, cross-rank integer sum, residual add and RMSNorm.  With more than one
+        rank the conversion of the summed accumulators, the residual add and the norm are one
+        kernel (same bits as the separate ones)."""
         c = self.cfg
         if self.group.size == 1:
             # nothing to exchange: the fused epilogue gives the same bits as int GEMM + epilogue
-            return ops.gemm_fxp(acts[0], weights[0], None, c.int_bits, c.frac_bits)
+            x = ops.gemm_fxp(acts[0], weights[0], None, c.int_bits, c.frac_bits)
+            return ops.rms_norm_fxp_residual(x, residual, norm_w, c.eps)
         accs = [ops.gemm_fxp_int(a, w, c.int_bits, c.frac_bits) for a, w in zip(acts, weights)]
         accs = self.group.all_reduce_int(accs)
-        return ops.gemm_fxp_epilogue(accs[0], None, c.dtype, c.frac_bits)
+        return ops.rms_norm_fxp_from_int(accs[0], residual, norm_w, None, c.eps, c.frac_bits)
 
     # ------------------------------------------------------------------ forward
     def forward(self, tokens, seq_ids, pos, qsl, seq_lens, max_q: int) -> torch.Tensor:
@@ -189,13 +193,9 @@ class LlamaDecoder:
         shards = [self.shards[r] for r in self.group.local_ranks]
         bt = self.block_table[: seq_lens.numel()]
         x = self.embed[tokens]
-        residual = None
+        residual = x.clone()
+        h = ops.rms_norm_fxp(x, self.norm_w[0], c.eps)
         for layer in range(c.layers):
-            if residual is None:
-                residual = x.clone()
-                h = ops.rms_norm_fxp(x, self.norm_w[2 * layer], c.eps)
-            else:
-                h = ops.rms_norm_fxp_residual(x, residual, self.norm_w[2 * layer], c.eps)
             outs = []
             for sh in shards:
                 qkv = ops.gemm_fxp(h, sh.qkv[layer], None, c.int_bits, c.frac_bits)
@@ -211,8 +211,7 @@ class LlamaDecoder:
                 ops.unified_attention_fxp(q, sh.kv_cache[layer], o, qsl, seq_lens, bt, max_q, None, True,
                                           None, c.int_bits, c.frac_bits, 0.0, 0, 0)
                 outs.append(o.reshape(T, self.qh * hd))
-            x = self._row_parallel(outs, [sh.o[layer] for sh in shards])
-            h = ops.rms_norm_fxp_residual(x, residual, self.norm_w[2 * layer + 1], c.eps)
+            h = self._row_parallel_norm(outs, [sh.o[layer] for sh in shards], residual, self.norm_w[2 * layer + 1])
             acts = []
             for sh in shards:
                 gu = ops.gemm_fxp(h, sh.gate_up[layer], None, c.int_bits, c.frac_bits)
@@ -221,8 +220,9 @@ class LlamaDecoder:
                 else:
                     f = gu.shape[1] // 2
                     acts.append((torch.nn.functional.silu(gu[:, :f].float()) * gu[:, f:].float()).to(c.dtype))
-            x = self._row_parallel(acts, [sh.down[layer] for sh in shards])
-        h = ops.rms_norm_fxp_residual(x, residual, self.norm_w[2 * c.layers], c.eps)
+            # the norm in front of the next layer (or, after the last layer, the final norm)
+            h = self._row_parallel_norm(acts, [sh.down[layer] for sh in shards], residual,
+                                        self.norm_w[2 * layer + 2])
         last = h[(qsl[1:] - 1).long()]
         parts = [ops.gemm_fxp(last, sh.lm_head, None, c.int_bits, c.frac_bits) for sh in shards]
         return self.group.all_gather_cols(parts)
