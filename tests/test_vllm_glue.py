@@ -214,6 +214,16 @@ def test_attention_impl_forward_equals_the_op_and_copies_back_other_dtypes():
     impl.forward(None, q.view(tokens, hq * d), None, None, kv, meta, output=out32)
     assert torch.equal(out32.view_as(expect), expect.float())
 
+    # a block table as wide as the model's maximum length (vLLM's): the backend hands the kernel
+    # only the pages of the longest live sequence, and the bits stay the same
+    wide = torch.zeros((bt.shape[0], 4 * bt.shape[1]), dtype=bt.dtype, device=bt.device)
+    wide[:, : bt.shape[1]] = bt
+    meta_w = types.SimpleNamespace(query_start_loc=qsl, seq_lens=sl, block_table=wide, max_query_len=max(qlens),
+                                   max_seq_len=max(lens))
+    out_w = torch.full((tokens, hq * d), float("nan"), device="cuda", dtype=q.dtype)
+    impl.forward(None, q.view(tokens, hq * d), None, None, kv, meta_w, output=out_w)
+    assert torch.equal(out_w.view_as(expect), expect)
+
     # the memory-profiling run (no metadata) returns zeros
     z = impl.forward(None, q.view(tokens, hq * d), None, None, kv, None)
     assert not z.any()

@@ -93,6 +93,7 @@ extern "C" int fxpr_attention(const void* q, const void* k_cache, const void* v_
   p.scale = (float)(1ull << frac_bits);
   p.inv_scale = 1.0f / p.scale;
   p.partial_max = nullptr; p.total_denom = nullptr; p.total_wv = nullptr; p.locks = nullptr;
+  p.status = status_word;
 
   // The tensor-core route merges its splits through distributed shared memory and needs
   // no scratch; only the CUDA-core route uses the caller's buffer.

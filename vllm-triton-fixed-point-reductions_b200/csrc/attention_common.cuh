@@ -17,6 +17,7 @@ struct AttnParams {
   long long* total_denom;      // [T, H]
   long long* total_wv;         // [T, H, D]
   int32_t* locks;              // [T, H]
+  int32_t* status;             // optional device status word (bounded waits, capacity refusals)
 };
 
 // Scratch carve-up for the split path: [partial_max | total_denom | total_wv | locks],

@@ -58,7 +58,10 @@ attn_decode_kernel(const AttnParams p, const MmaAttnShape sh) {
   const int per_rank = (t_last - t_first + S - 1) / S;
   const int t0 = min(t_last, t_first + rank * per_rank);
   const int t1 = min(t_last, t0 + per_rank);
-  if (per_rank * kTileN > sh.stash_keys) return;   // stash sized from the block-table width
+  if (per_rank * kTileN > sh.stash_keys) {          // the host sizes the stash from the block-table width
+    if (threadIdx.x == 0 && p.status) atomicExch(p.status, FXPR_ERR_SCRATCH);
+    return;                                          // the same decision in every CTA of the cluster
+  }
 
   int r_tok[2], r_kend[2], r_kbeg[2]; float r_slope[2];
 #pragma unroll

@@ -55,7 +55,10 @@ attn_mma_kernel(const AttnParams p, const MmaAttnShape sh) {
   const int t1 = min(t_last, t0 + per_rank);
 
   // the stash is sized from the block table's width on the host; never index past it
-  if (STASH && per_rank * kTileN > sh.stash_keys) return;
+  if (STASH && per_rank * kTileN > sh.stash_keys) {
+    if (threadIdx.x == 0 && p.status) atomicExch(p.status, FXPR_ERR_SCRATCH);
+    return;
+  }
 
   // ---- the two rows this thread owns in the MMA accumulator layout ------------------
   int r_tok[2], r_head[2], r_kend[2], r_kbeg[2]; bool r_valid[2]; float r_slope[2];

@@ -121,6 +121,65 @@ __device__ __forceinline__ float exp2_det(float t) {
 // log2(e) as the fp32 the host oracle uses (1.4426950408889634 rounded).
 #define FXPR_LOG2E_F32 __int_as_float(0x3fb8aa3b)
 
+// ---- two fp32 lanes per instruction (add/sub/mul/fma .f32x2: IEEE round-to-nearest per lane) ----
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_sub(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+
+// exp2_det of two non-positive (or NaN) arguments at once, for callers that only use the
+// result through float_to_fixed with at most 32 fraction bits.  Same operations on every lane as
+// exp2_det, with two differences that cannot change a rounded Q value: arguments below -126 (and
+// NaN) are clamped to -126 instead of returning 0 (2^-126 * 2^32 still rounds to 0), and
+// n = rint(t) is taken from the mantissa of t + 1.5 * 2^23 (exact for |t| < 2^22), whose low bits
+// also give the exponent field of 2^n without a float-to-int conversion.
+__device__ __forceinline__ uint64_t exp2_det_nonpos_pair(float t0, float t1) {
+  const float m = __uint_as_float(0x4B400000u);
+  const uint64_t magic = f2_pack(m, m);
+  const uint64_t t = f2_pack(fmaxf(t0, -126.0f), fmaxf(t1, -126.0f));
+  const uint64_t r = f2_add(t, magic);               // bits: 0x4B400000 + n
+  const uint64_t n = f2_sub(r, magic);
+  const uint64_t f = f2_sub(t, n);
+#define FXPR_C2(bits) f2_pack(__int_as_float(bits), __int_as_float(bits))
+  uint64_t p = FXPR_C2(0x377fe5fe);
+  p = f2_add(f2_mul(p, f), FXPR_C2(0x39218489));
+  p = f2_add(f2_mul(p, f), FXPR_C2(0x3aaec3ff));
+  p = f2_add(f2_mul(p, f), FXPR_C2(0x3c1d955b));
+  p = f2_add(f2_mul(p, f), FXPR_C2(0x3d635847));
+  p = f2_add(f2_mul(p, f), FXPR_C2(0x3e75fdf0));
+  p = f2_add(f2_mul(p, f), FXPR_C2(0x3f317218));
+  p = f2_add(f2_mul(p, f), FXPR_C2(0x3f800000));
+#undef FXPR_C2
+  // (0x4B400000 + n + 127) << 23 keeps only n + 127 in the exponent field
+  const uint32_t lo = ((uint32_t)r + 127u) << 23, hi = ((uint32_t)(r >> 32) + 127u) << 23;
+  const uint64_t two_n = ((uint64_t)hi << 32) | lo;
+  return f2_mul(p, two_n);
+}
+
 // ---- deterministic natural log of a positive, normal fp32 ---------------------------
 // fp64 with + - * / only: v = m 2^e, m in [sqrt(1/2), sqrt(2)); s = (m-1)/(m+1);
 // log m = 2 s (1 + s^2/3 + ... + s^18/19).  Result rounded to fp32.

@@ -83,13 +83,22 @@ log_softmax_kernel(const T* __restrict__ x, float* __restrict__ y, int cols, int
     if (wide_q) acc += (unsigned long long)float_to_fixed<64>(e, scale);
     else acc += (unsigned long long)(long long)float_to_fixed<32>(e, scale);
   };
+  // two logits per instruction (packed sub/mul/add round each lane as the scalar forms do)
+  const uint64_t gmax2 = f2_pack(gmax, gmax), log2e2 = f2_pack(FXPR_LOG2E_F32, FXPR_LOG2E_F32);
+  auto add_two = [&](float a, float b) {
+    float t0, t1, e0, e1;
+    f2_unpack(f2_mul(f2_sub(f2_pack(a, b), gmax2), log2e2), t0, t1);
+    f2_unpack(exp2_det_nonpos_pair(t0, t1), e0, e1);
+    if (wide_q) acc += (unsigned long long)float_to_fixed<64>(e0, scale) + (unsigned long long)float_to_fixed<64>(e1, scale);
+    else acc += (unsigned long long)(long long)float_to_fixed<32>(e0, scale) + (unsigned long long)(long long)float_to_fixed<32>(e1, scale);
+  };
   if (CACHE) {
     // four independent exp chains per thread and iteration (the polynomial is a long
     // dependent chain; integer addition makes the visiting order irrelevant)
     const int n4 = len / 4;
     for (int c = threadIdx.x; c < n4; c += blockDim.x) {
       const float4 v = *reinterpret_cast<const float4*>(slice + c * 4);
-      add_one(v.x); add_one(v.y); add_one(v.z); add_one(v.w);
+      add_two(v.x, v.y); add_two(v.z, v.w);
     }
     for (int i = n4 * 4 + threadIdx.x; i < len; i += blockDim.x) add_one(slice[i]);
   } else {
@@ -184,16 +193,28 @@ log_softmax_reg_kernel(const T* __restrict__ x, float* __restrict__ y, int cols,
   uint32_t acc32 = 0, cnt = 0;
   const bool magic_ok = scale <= 2097152.0f;
   const float magic = __uint_as_float(0x4B400000u);
+  const uint64_t gmax2 = f2_pack(gmax, gmax), log2e2 = f2_pack(FXPR_LOG2E_F32, FXPR_LOG2E_F32);
+  const uint64_t scale2 = f2_pack(scale, scale), magic2 = f2_pack(magic, magic);
 #pragma unroll
   for (int k = 0; k < NV; ++k) {
     const int c = k * kLsmThreads + (int)threadIdx.x;
     if (c < nvec) {
+      // two logits per instruction: packed sub/mul/add carry the same IEEE roundings per lane
 #pragma unroll
-      for (int j = 0; j < VEC; ++j) {
-        const float e = exp2_det(__fmul_rn(__fsub_rn(vals[k * VEC + j], gmax), FXPR_LOG2E_F32));
-        if (magic_ok) acc32 += __float_as_uint(__fmaf_rn(e, scale, magic));
-        else if (wide_q) acc += (unsigned long long)float_to_fixed<64>(e, scale);
-        else acc += (unsigned long long)(long long)float_to_fixed<32>(e, scale);
+      for (int j = 0; j < VEC; j += 2) {
+        const uint64_t d = f2_mul(f2_sub(f2_pack(vals[k * VEC + j], vals[k * VEC + j + 1]), gmax2), log2e2);
+        float t0, t1;
+        f2_unpack(d, t0, t1);
+        const uint64_t e2 = exp2_det_nonpos_pair(t0, t1);
+        if (magic_ok) {
+          const uint64_t q = f2_fma(e2, scale2, magic2);
+          acc32 += (uint32_t)q + (uint32_t)(q >> 32);
+        } else {
+          float e0, e1;
+          f2_unpack(e2, e0, e1);
+          if (wide_q) acc += (unsigned long long)float_to_fixed<64>(e0, scale) + (unsigned long long)float_to_fixed<64>(e1, scale);
+          else acc += (unsigned long long)(long long)float_to_fixed<32>(e0, scale) + (unsigned long long)(long long)float_to_fixed<32>(e1, scale);
+        }
       }
       cnt += VEC;
     }
@@ -209,6 +230,7 @@ log_softmax_reg_kernel(const T* __restrict__ x, float* __restrict__ y, int cols,
   }
   __syncthreads();
   const float lg = bc_log;
+  const uint64_t lg2 = f2_pack(lg, lg);
 
 #pragma unroll
   for (int k = 0; k < NV; ++k) {
@@ -217,10 +239,8 @@ log_softmax_reg_kernel(const T* __restrict__ x, float* __restrict__ y, int cols,
 #pragma unroll
       for (int j4 = 0; j4 < VEC / 4; ++j4) {
         float4 o;
-        o.x = __fsub_rn(__fsub_rn(vals[k * VEC + j4 * 4 + 0], gmax), lg);
-        o.y = __fsub_rn(__fsub_rn(vals[k * VEC + j4 * 4 + 1], gmax), lg);
-        o.z = __fsub_rn(__fsub_rn(vals[k * VEC + j4 * 4 + 2], gmax), lg);
-        o.w = __fsub_rn(__fsub_rn(vals[k * VEC + j4 * 4 + 3], gmax), lg);
+        f2_unpack(f2_sub(f2_sub(f2_pack(vals[k * VEC + j4 * 4 + 0], vals[k * VEC + j4 * 4 + 1]), gmax2), lg2), o.x, o.y);
+        f2_unpack(f2_sub(f2_sub(f2_pack(vals[k * VEC + j4 * 4 + 2], vals[k * VEC + j4 * 4 + 3]), gmax2), lg2), o.z, o.w);
         *reinterpret_cast<float4*>(yr + c * VEC + j4 * 4) = o;
       }
     }

@@ -159,12 +159,23 @@ class DeterministicAttentionImpl(AttentionImpl):
         if self.alibi_slopes is not None and self.alibi_slopes.device != q.device:
             self.alibi_slopes = self.alibi_slopes.to(q.device)
 
+        # The launcher sizes its KV-split count and the decode kernel's score stash from the
+        # block table's width, the only context bound the op's signature carries.  vLLM's table
+        # is as wide as the model's maximum length; the metadata knows the longest live
+        # sequence, so hand the kernel a view of just that many pages.
+        block_table = attn_metadata.block_table
+        max_seq_len = getattr(attn_metadata, "max_seq_len", None)
+        if max_seq_len and block_table.dim() == 2:
+            pages = -(-int(max_seq_len) // kv_cache.shape[2])
+            if 0 < pages < block_table.shape[1]:
+                block_table = block_table[:, :pages]
+
         q_in = q if q.dtype == kv_cache.dtype else q.to(kv_cache.dtype)
         o_in = out if out.dtype == q_in.dtype else torch.empty_like(out, dtype=q_in.dtype)
         torch.ops.fxpr.unified_attention_fxp(
             q_in, kv_cache, o_in,
             _as_int32(attn_metadata.query_start_loc), _as_int32(attn_metadata.seq_lens),
-            attn_metadata.block_table, int(attn_metadata.max_query_len), self.alibi_slopes,
+            block_table, int(attn_metadata.max_query_len), self.alibi_slopes,
             True, float(self.scale), int(self.fxp_int_bits), int(self.fxp_frac_bits),
             float(self.logits_soft_cap), int(self.window_size),
             0,  # let the launcher pick the KV-split count
