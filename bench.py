@@ -403,6 +403,10 @@ def bench_llama(dev, dist, world, peaks, batch=64, prompt_len=1024, gen=256):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return out, float(ms.item())
 
+    if dist is not None and os.environ.get("FXPR_BENCH_NCCL_EXCHANGE") != "1":
+        # decode-sized batches exchange through the peer-memory reduce + norm kernel (same bits);
+        # the prefill below is too large for its buffers and takes the ncclAllReduce path
+        model.enable_peer_reduce()
     logits, prefill_ms = timed(lambda: model.prefill(prompts))
     d_prefill = _digest(logits)
     state = {"tok": model.greedy(logits), "logits": logits}
@@ -427,6 +431,10 @@ def bench_llama(dev, dist, world, peaks, batch=64, prompt_len=1024, gen=256):
         graph_error = repr(e)[:200]
         _, decode_ms = timed(decode_all)
         launch = "python-launched ops"
+    tp_scaling = None
+    if dist is not None and graph_error is None:
+        tp_scaling = _tp_scaling(model, cfg, dev, dist, world, timed, state, prompts, prompt_len, gen,
+                                 decode_ms / gen)
     weights_gb = (cfg.layers * (cfg.hidden * (cfg.q_heads + 2 * cfg.kv_heads) * cfg.head_dim
                                 + cfg.q_heads * cfg.head_dim * cfg.hidden + 3 * cfg.hidden * cfg.ffn)
                   + cfg.hidden * cfg.vocab) * 2 / 1e9
@@ -440,10 +448,65 @@ def bench_llama(dev, dist, world, peaks, batch=64, prompt_len=1024, gen=256):
         "logits_digest_prefill": d_prefill, "logits_digest_last": _digest(state["logits"]),
         "last_tokens_digest": int((state["tok"] * (torch.arange(batch, device=dev) + 1)).sum().item()),
         "build_s": build_s,
-        "launch": launch, "graph_error": graph_error,
+        "launch": launch, "graph_error": graph_error, "tp_scaling": tp_scaling,
         "note": "digests are equal across TP degrees when the integer all-reduce keeps the logits "
                 "bit-identical",
     }
+
+
+def _tp_scaling(model, cfg, dev, dist, world, timed, state, prompts, prompt_len, gen, step_ms, short=64):
+    """How the decode step divides at TP = world.  The last `short` positions are decoded again
+    (deterministic: same tokens, same KV prefix) with (a) ncclAllReduce + norm kernel, (b) the
+    peer-memory reduce + norm kernel -- their logits digests must agree -- and (c) no exchange at
+    all (wrong results, same kernels), which gives the collective share; a TP = 1 copy of the
+    model on this GPU gives the speed-up.  Runs after the headline digests are taken."""
+    from fxpr_vllm.llama_decoder import LlamaDecoder, LocalGroup
+
+    start = prompt_len + gen - short
+    tok0 = state["tok"].clone()
+
+    def run():
+        model.capture_decode(tok0, start)
+
+        def replay():
+            for _ in range(short):
+                model.replay_decode()
+
+        _, ms = timed(replay)
+        return ms / short, _digest(model._g_logits)
+
+    peer, model.peer = model.peer, None
+    nccl_ms, d_nccl = run()
+    model.peer = peer
+    peer_ms, d_peer = run() if peer is not None else (None, None)
+    model.group.skip_collectives = True
+    try:
+        no_coll, _ = run()
+    finally:
+        model.group.skip_collectives = False
+    del model._graph
+    one = LlamaDecoder(cfg, LocalGroup(1), dev, seed=0, max_seqs=prompts.shape[0], max_len=prompt_len + gen)
+    tok = one.greedy(one.prefill(prompts))
+    one.capture_decode(tok, prompt_len)
+
+    def replay_one():
+        for _ in range(short):
+            one.replay_decode()
+
+    _, ms1 = timed(replay_one)
+    tp1 = ms1 / short
+    del one
+    torch.cuda.empty_cache()
+    return {"tp": world, "ms_per_step": step_ms,
+            "exchange": "peer-memory reduce+norm kernel" if peer is not None else "ncclAllReduce + norm kernel",
+            "ms_per_step_nccl_exchange": nccl_ms, "ms_per_step_peer_exchange": peer_ms,
+            "digests_equal_nccl_vs_peer": None if peer is None else bool(d_nccl == d_peer),
+            "ms_per_step_without_collectives": no_coll,
+            "collective_share": max(0.0, 1.0 - no_coll / step_ms),
+            "collective_share_nccl_exchange": max(0.0, 1.0 - no_coll / nccl_ms),
+            "tp1_ms_per_step": tp1, "speedup_vs_tp1": tp1 / step_ms,
+            "how": f"{short} replays each over the last {short} positions; 'without collectives' skips the "
+                   "exchanges (results discarded); TP=1 is the same model unsharded on this GPU"}
 
 
 def bench_others(dev, peaks, L, syn):

@@ -104,6 +104,44 @@ int fxpr_rms_norm_from_int(const void* acc, int int_bits, const void* bias,
                            int gemm_frac_bits, int frac_bits, void* stream);
 
 /*
+ * Tensor-parallel row-parallel layers without a library collective: the cross-rank integer
+ * sum, fxpr_rms_norm_from_int's arithmetic and the distribution of the result as ONE kernel
+ * per rank over peer-mapped memory (plain loads and stores over NVLink; no multicast).  Same
+ * bits as ncclAllReduce(sum) on the accumulators followed by fxpr_rms_norm_from_int, for any
+ * rank count.  No counterpart in the reference (vLLM's float all-reduce follows its
+ * quant_method.apply, vllm/model_executor/layers/linear.py); the integer ncclAllReduce of
+ * fxpr_vllm/tp.py stays the default exchange.
+ *
+ * Each rank owns one buffer: accumulators [max_rows, hidden] int{int_bits} | residual
+ * [max_rows, hidden] | output [max_rows, hidden] (io dtype) | 32 flag words, at the offsets
+ * fxpr_tp_buffer_bytes reports.  fxpr_tp_alloc makes a zeroed cudaMalloc buffer on the current
+ * device and its 64-byte CUDA IPC handle; fxpr_tp_open maps a peer's handle into the current
+ * device's context (lazy peer access); fxpr_tp_close / fxpr_tp_free undo them.
+ *
+ * fxpr_tp_reduce_norm: peer_bases[world] are the buffers as mapped in THIS process
+ * (peer_bases[rank] is the local one); ctl points to two zero-initialised 32-bit words in local
+ * device memory that the kernel owns (call counter, CTA arrivals).  Before the call this
+ * rank's accumulators [rows, hidden] are complete in its buffer (same stream) and its residual
+ * rows are current; after it every rank's residual and output regions hold all rows.  Rank r
+ * reduces rows [r * ceil(rows / world), ...).  All ranks must issue the same sequence of calls.
+ * Waits last at most timeout_cycles SM clocks (<= 0: about a second); when one runs out the
+ * kernel writes FXPR_ERR_TIMEOUT to *status and stops touching peer memory; the buffers must
+ * then be re-created.  int_bits 32 or 64; hidden a multiple of 4, at most 16384.
+ */
+int fxpr_tp_buffer_bytes(int64_t max_rows, int64_t hidden, int int_bits, int dtype,
+                         int64_t* acc_offset, int64_t* residual_offset, int64_t* y_offset,
+                         int64_t* flags_offset, int64_t* total);
+int fxpr_tp_alloc(int64_t bytes, void** ptr, void* handle64);
+int fxpr_tp_open(const void* handle64, void** ptr);
+int fxpr_tp_close(void* ptr);
+int fxpr_tp_free(void* ptr);
+int fxpr_tp_reduce_norm(const void* const* peer_bases, int world, int rank, void* ctl,
+                        int64_t acc_offset, int64_t residual_offset, int64_t y_offset,
+                        int64_t flags_offset, int int_bits, const void* bias, const void* weight,
+                        int dtype, int64_t rows, int64_t hidden, float eps, int gemm_frac_bits,
+                        int frac_bits, int64_t timeout_cycles, int32_t* status, void* stream);
+
+/*
  * Row-wise log-softmax of a contiguous [rows, cols] matrix into fp32:
  * y = (x - max) - log(sum_int64(Q(exp(x - max)))).  x_dtype in
  * {FXPR_F16, FXPR_BF16, FXPR_F32}.  No counterpart in the reference (the

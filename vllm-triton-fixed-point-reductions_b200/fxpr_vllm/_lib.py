@@ -413,11 +413,17 @@ def pick_split_k(M: int, N: int, K: int, k_tile: int, int_bits: int, num_sms: in
     return split
 
 
-def _gemm_common(a, b, bias, int_bits, frac_bits, want_c: bool, want_int: bool):
+def _gemm_common(a, b, bias, int_bits, frac_bits, want_c: bool, want_int: bool, out_int=None):
     M, K = a.shape
     N = b.shape[1]
     c = torch.empty((M, N), device=a.device, dtype=a.dtype) if want_c else None
-    c_int = torch.empty((M, N), device=a.device, dtype=_INT_DTYPE[int_bits]) if want_int else None
+    if out_int is not None:
+        if (out_int.shape != (M, N) or out_int.dtype != _INT_DTYPE[int_bits] or not out_int.is_contiguous()
+                or out_int.device != a.device):
+            raise ValueError("gemm_fxp_int_into: out must be a contiguous [M, N] tensor of the accumulator type")
+        c_int = out_int
+    else:
+        c_int = torch.empty((M, N), device=a.device, dtype=_INT_DTYPE[int_bits]) if want_int else None
     if M == 0 or N == 0:
         return c, c_int
     if a.dtype not in _IO_DTYPES or b.dtype != a.dtype:
@@ -464,6 +470,13 @@ def gemm_fxp_run(a, b, bias, int_bits, fxp_frac_bits):
 def gemm_fxp_int_run(a, b, int_bits, fxp_frac_bits):
     _, c_int = _gemm_common(a, b, None, int_bits, fxp_frac_bits, False, True)
     return c_int
+
+
+def gemm_fxp_int_into(a, b, out, int_bits, fxp_frac_bits):
+    """``gemm_fxp_int`` into a caller-owned accumulator tensor (for example a peer-mapped
+    buffer that other ranks read)."""
+    _gemm_common(a, b, None, int_bits, fxp_frac_bits, False, True, out_int=out)
+    return out
 
 
 def gemm_fxp_epilogue_run(c_int, bias, out_dtype, fxp_frac_bits):

@@ -67,6 +67,13 @@ SIGNATURES = {
     "fxpr_rms_norm": (_i, [_vp, _vp, _vp, _vp, _i, _i64, _i64, _f, _i, _vp]),
     "fxpr_rms_norm_from_int": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _i, _i64, _i64, _f, _i, _i, _vp]),
     "fxpr_log_softmax": (_i, [_vp, _i, _vp, _i64, _i64, _i, _vp]),
+    "fxpr_tp_buffer_bytes": (_i, [_i64, _i64, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "fxpr_tp_alloc": (_i, [_i64, _vp, _vp]),
+    "fxpr_tp_open": (_i, [_vp, _vp]),
+    "fxpr_tp_close": (_i, [_vp]),
+    "fxpr_tp_free": (_i, [_vp]),
+    "fxpr_tp_reduce_norm": (_i, [_vp, _i, _i, _vp, _i64, _i64, _i64, _i64, _i, _vp, _vp, _i, _i64, _i64, _f,
+                                 _i, _i, _i64, _vp, _vp]),
     "fxpr_rope_kv_write": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _i64, _i, _i, _i, _i,
                                 _i64, _i64, _i64, _i64, _vp]),
     "fxpr_silu_mul": (_i, [_vp, _i, _vp, _i64, _i64, _vp]),

@@ -25,7 +25,7 @@ import torch
 import torch.distributed as dist
 
 from . import library_ops as ops
-from ._lib import BLOCK_K_BY_DTYPE, rope_kv_write, silu_mul
+from ._lib import BLOCK_K_BY_DTYPE, gemm_fxp_int_into, rope_kv_write, silu_mul
 from .config import get_runtime_config
 from .tp import check_shardable
 
@@ -72,15 +72,20 @@ class DistGroup:
         self.group = group
         self.size = dist.get_world_size(group)
         self.local_ranks = [dist.get_rank(group)]
+        # timing aid: with this set the exchanges are left out (results are then wrong, the
+        # kernels and their shapes are unchanged), so a step's collective share can be measured
+        self.skip_collectives = False
 
     def all_reduce_int(self, parts):
-        if self.size > 1:
+        if self.size > 1 and not self.skip_collectives:
             dist.all_reduce(parts[0], op=dist.ReduceOp.SUM, group=self.group)
         return parts
 
     def all_gather_cols(self, parts):
         if self.size == 1:
             return parts[0]
+        if self.skip_collectives:
+            return torch.cat([parts[0]] * self.size, dim=-1)
         out = [torch.empty_like(parts[0]) for _ in range(self.size)]
         dist.all_gather(out, parts[0].contiguous(), group=self.group)
         return torch.cat(out, dim=-1)
@@ -156,6 +161,19 @@ class LlamaDecoder:
         inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, hd, 2, device=dev, dtype=torch.float32) / hd))
         ang = torch.arange(max_len, device=dev, dtype=torch.float32)[:, None] * inv[None, :]
         self.cos, self.sin = ang.cos(), ang.sin()
+        self.peer = None
+
+    def enable_peer_reduce(self, max_rows: int | None = None) -> None:
+        """Batches of at most ``max_rows`` tokens (decode steps) exchange through the
+        peer-memory reduce + norm kernel instead of ``ncclAllReduce`` + a norm kernel.  Same
+        bits; collective: every rank of the group must call it."""
+        from .tp_fused import PeerReduceNorm
+
+        if not isinstance(self.group, DistGroup) or self.group.size == 1:
+            return
+        c = self.cfg
+        self.peer = PeerReduceNorm(max_rows or self.max_seqs, c.hidden, c.dtype, c.int_bits,
+                                   group=self.group.group, device=self.device)
 
     # ------------------------------------------------------------------ pieces
     def _rope(self, x: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
@@ -180,6 +198,11 @@ class LlamaDecoder:
             # nothing to exchange: the fused epilogue gives the same bits as int GEMM + epilogue
             x = ops.gemm_fxp(acts[0], weights[0], None, c.int_bits, c.frac_bits)
             return ops.rms_norm_fxp_residual(x, residual, norm_w, c.eps)
+        rows = acts[0].shape[0]
+        if self.peer is not None and rows <= self.peer.max_rows and not self.group.skip_collectives:
+            # `residual` is the peer buffer's residual window (see forward)
+            gemm_fxp_int_into(acts[0], weights[0], self.peer.acc[:rows], c.int_bits, c.frac_bits)
+            return self.peer.reduce_norm(rows, norm_w, None, c.eps, c.frac_bits)
         accs = [ops.gemm_fxp_int(a, w, c.int_bits, c.frac_bits) for a, w in zip(acts, weights)]
         accs = self.group.all_reduce_int(accs)
         return ops.rms_norm_fxp_from_int(accs[0], residual, norm_w, None, c.eps, c.frac_bits)
@@ -193,7 +216,11 @@ class LlamaDecoder:
         shards = [self.shards[r] for r in self.group.local_ranks]
         bt = self.block_table[: seq_lens.numel()]
         x = self.embed[tokens]
-        residual = x.clone()
+        if self.peer is not None and T <= self.peer.max_rows:
+            residual = self.peer.residual[:T]       # every rank's copy is kept current by the kernel
+            residual.copy_(x)
+        else:
+            residual = x.clone()
         h = ops.rms_norm_fxp(x, self.norm_w[0], c.eps)
         for layer in range(c.layers):
             outs = []
