@@ -120,19 +120,8 @@ static int launch_mma(const AttnParams& p, const MmaAttnShape& sh, cudaStream_t 
     e = cudaFuncSetAttribute(k, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
     if (e != cudaSuccess) { set_last_error("attention_mma cluster attribute", e); return FXPR_ERR_CUDA; }
   }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)p.num_splits, (unsigned)(sh.num_q_blocks * p.num_kv_heads), (unsigned)p.num_reqs);
-  cfg.blockDim = dim3(NW * 32);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = s;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = (unsigned)p.num_splits;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  e = cudaLaunchKernelEx(&cfg, k, p, sh);
+  e = launch_pdl(k, dim3((unsigned)p.num_splits, (unsigned)(sh.num_q_blocks * p.num_kv_heads), (unsigned)p.num_reqs),
+                 dim3(NW * 32), smem, s, (unsigned)p.num_splits, p, sh);
   if (e != cudaSuccess) { set_last_error("attention_mma launch", e); return FXPR_ERR_CUDA; }
   return check_launch("attention_mma");
 }
@@ -149,19 +138,8 @@ static int launch_decode(const AttnParams& p, const MmaAttnShape& sh, cudaStream
     e = cudaFuncSetAttribute(k, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
     if (e != cudaSuccess) { set_last_error("attention_decode cluster attribute", e); return FXPR_ERR_CUDA; }
   }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)p.num_splits, (unsigned)(sh.num_q_blocks * p.num_kv_heads), (unsigned)p.num_reqs);
-  cfg.blockDim = dim3(NW * 32);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = s;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = (unsigned)p.num_splits;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  e = cudaLaunchKernelEx(&cfg, k, p, sh);
+  e = launch_pdl(k, dim3((unsigned)p.num_splits, (unsigned)(sh.num_q_blocks * p.num_kv_heads), (unsigned)p.num_reqs),
+                 dim3(NW * 32), smem, s, (unsigned)p.num_splits, p, sh);
   if (e != cudaSuccess) { set_last_error("attention_decode launch", e); return FXPR_ERR_CUDA; }
   return check_launch("attention_decode");
 }

@@ -34,6 +34,8 @@ attn_decode_kernel(const AttnParams p, const MmaAttnShape sh) {
   float* stash_s = reinterpret_cast<float*>(den_s + NW * 16);
   long long* wv_s = reinterpret_cast<long long*>(stage_s);        // [16][HD], reuses the stages
 
+  pdl_launch_dependents();
+  pdl_wait();
   cg::cluster_group cluster = cg::this_cluster();
   const int S = gridDim.x, rank = blockIdx.x;
   const int hkv = p.num_kv_heads;

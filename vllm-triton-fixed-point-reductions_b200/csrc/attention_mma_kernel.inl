@@ -26,6 +26,8 @@ attn_mma_kernel(const AttnParams p, const MmaAttnShape sh) {
   long long* den_s = reinterpret_cast<long long*>(rmax_s + BM);                   // [BM]
   float* stash_s = reinterpret_cast<float*>(den_s + BM);                          // decode only
   long long* wv_s = reinterpret_cast<long long*>(stage_s);        // [BM][HD], reuses the stages
+  pdl_launch_dependents();
+  pdl_wait();
 
   cg::cluster_group cluster = cg::this_cluster();
   const int S = gridDim.x;

@@ -1,4 +1,5 @@
 // Status strings, per-thread error text and launch checking for the C ABI.
+#include <cstdlib>
 #include <stdio.h>
 #include <string.h>
 
@@ -28,6 +29,14 @@ int check_launch(const char* what) {
     return FXPR_ERR_CUDA;
   }
   return FXPR_OK;
+}
+
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("FXPR_NO_PDL");
+    return !(v && v[0] == '1');
+  }();
+  return on;
 }
 
 }  // namespace fxpr

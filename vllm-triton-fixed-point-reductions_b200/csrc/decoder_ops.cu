@@ -23,6 +23,8 @@ rope_kv_write_kernel(const T* __restrict__ qkv, const float* __restrict__ cos_t,
                      int64_t kv_sblock, int64_t kv_skv, int64_t kv_sslot, int64_t kv_shead) {
   // grid: (token, slice of the work): blockIdx.y strides over the head items so that a decode
   // step (64 tokens) still fills the GPU
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t tok = blockIdx.x;
   const int part = blockIdx.y, parts = gridDim.y;
   const int half = head_dim / 2;
@@ -68,6 +70,8 @@ struct alignas(sizeof(T) * VEC) ActPack {
 template <typename T, int VEC>
 __global__ void __launch_bounds__(256)
 silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t rows, int64_t f) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t fv = f / VEC;                      // launcher guarantees f % VEC == 0
   const int64_t n = rows * fv;
   for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (int64_t)gridDim.x * blockDim.x) {
@@ -91,8 +95,8 @@ static void launch_silu(const void* gu, void* out, int64_t rows, int64_t f, cuda
   const bool vec = (f % V == 0) && ((((uintptr_t)gu | (uintptr_t)out) & 15) == 0);
   const int64_t n = rows * (vec ? f / V : f);
   const unsigned grid = (unsigned)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
-  if (vec) silu_mul_kernel<T, V><<<grid, 256, 0, s>>>((const T*)gu, (T*)out, rows, f);
-  else silu_mul_kernel<T, 1><<<grid, 256, 0, s>>>((const T*)gu, (T*)out, rows, f);
+  if (vec) (void)launch_pdl(silu_mul_kernel<T, V>, dim3(grid), dim3(256), 0, s, 1u, (const T*)gu, (T*)out, rows, f);
+  else (void)launch_pdl(silu_mul_kernel<T, 1>, dim3(grid), dim3(256), 0, s, 1u, (const T*)gu, (T*)out, rows, f);
 }
 
 }  // namespace fxpr
@@ -118,7 +122,7 @@ extern "C" int fxpr_rope_kv_write(const void* qkv, int dtype, const float* cos_t
   while (parts > 1 && tokens * parts > 148 * 8) parts = (parts + 1) / 2;
   const dim3 grid((unsigned)tokens, (unsigned)parts);
 #define FXPR_ROPE(TT)                                                                                  \
-  rope_kv_write_kernel<TT><<<grid, 256, 0, s>>>(                                                       \
+  (void)launch_pdl(rope_kv_write_kernel<TT>, grid, dim3(256), 0, s, 1u,                                \
       (const TT*)qkv, cos_table, sin_table, positions, seq_ids, block_table, bt_stride, (TT*)q_out,    \
       (TT*)kv_cache, q_heads, kv_heads, head_dim, page_size, kv_sblock, kv_skv, kv_sslot, kv_shead)
   switch (dtype) {

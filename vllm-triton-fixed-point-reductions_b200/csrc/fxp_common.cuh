@@ -23,6 +23,52 @@ int check_launch(const char* what);
 
 inline int ceil_div_i(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }
 
+// ---- programmatic dependent launch ------------------------------------------------
+// Decode steps are chains of short kernels, each waiting for the one before it.  Launched with
+// the programmatic-stream-serialization attribute, a kernel's CTAs may start (barrier setup,
+// tensor-memory allocation, descriptor prefetch) while the previous kernel is still running;
+// pdl_wait() then blocks until every earlier kernel of the stream has completed and its writes
+// are visible.  Rules every such kernel keeps: no global-memory access that depends on (or is
+// read by) an earlier kernel before pdl_wait(), and every CTA calls pdl_wait().  Without the
+// attribute both instructions do nothing.  FXPR_NO_PDL=1 in the environment turns the
+// attribute off.
+bool pdl_enabled();
+
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+// cudaLaunchKernelEx with the attribute (and an optional cluster width along x).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, unsigned cluster_x, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  if (pdl_enabled()) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (cluster_x > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = cluster_x;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 // ---- integer type by width -----------------------------------------------------
 template <int BITS> struct IntOf;
 template <> struct IntOf<16> { using type = int16_t; };

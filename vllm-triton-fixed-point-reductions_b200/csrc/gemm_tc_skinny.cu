@@ -62,6 +62,7 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_co
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+  pdl_launch_dependents();                               // the next kernel may start its own setup
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8u * s, 1); mbar_init(empty0 + 8u * s, 1); }
     for (int b = 0; b < kSkGroups; ++b) { mbar_init(tfull0 + 8u * b, 1); mbar_init(tempty0 + 8u * b, EPIW); }
@@ -77,6 +78,9 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_co
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // barriers, tensor memory and descriptors are set up; from here on the kernel reads what
+  // earlier kernels of the stream wrote
+  pdl_wait();
 
   const int tiles_n = p.tiles_n;                         // 128-column tiles; one row tile (M <= 64)
   const int items = tiles_n * p.split_k;
@@ -92,7 +96,11 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_co
   if (warp == 0) {
     // ------------------------------ TMA producer --------------------------------
     const bool wk = p.b_kmajor != 0;                     // weights given as an (N, K) row-major view
-    int stage = 0; uint32_t phase = 1;
+    // A stage is free again when the MMAs that read it are done, which is also when their
+    // accumulator group is full: the issuer signals both with ONE commit (a tcgen05.commit costs
+    // ~260 clocks of the issuing thread), so super-stage j waits for the group barrier of
+    // super-stage j - STAGES.
+    int stage = 0; int wgrp = 0; uint32_t wphase = 0; int issued = 0;
     for (int item = first_item; item < items; item += item_step) {
       const int n0 = (item / p.split_k) * 128;
       const int ks = item % p.split_k;
@@ -102,7 +110,11 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_co
         const int ka = pairs ? (ks + (2 * ss) * p.split_k) * 64 : (ks + ss * p.split_k) * 128;
         const int kb = pairs ? ka + p.split_k * 64 : ka + 64;
         const bool two = pairs ? (2 * ss + 1 < n_kt) : true;
-        if (!__all_sync(0xffffffffu, mbar_wait(empty0 + 8u * stage, phase, abort_flag))) goto producer_done;
+        if (issued >= STAGES) {
+          if (!__all_sync(0xffffffffu, mbar_wait(tfull0 + 8u * wgrp, wphase, abort_flag))) goto producer_done;
+          if (++wgrp == ngroup) { wgrp = 0; wphase ^= 1; }
+        }
+        ++issued;
         const uint32_t fb = full0 + 8u * stage;
         const uint32_t sw = smem_base + stage * kSkSSBytes;
         const uint32_t sx = sw + kSkWBytes;
@@ -119,7 +131,7 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_co
           }
         }
         __syncwarp();
-        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        if (++stage == STAGES) stage = 0;
       }
     }
   producer_done:;
@@ -158,8 +170,7 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_co
             for (int i = 0; i < 4; ++i)
               umma_f16(d1, wd + kHalfW + i * wks, xd + kHalfX + i * 2, idesc, (i || !pairs) ? 1u : 0u);
           }
-          umma_commit(empty0 + 8u * stage);
-          umma_commit(tfull0 + 8u * grp);
+          umma_commit(tfull0 + 8u * grp);              // stage consumed AND accumulator group full
         }
         __syncwarp();
         if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -245,19 +256,8 @@ static int launch_skinny_cluster(const CUtensorMap& mw, const CUtensorMap& mx, T
   }
   p.tiles_m = 1;
   p.tiles_n = (p.N + 127) / 128;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)p.split_k, (unsigned)p.tiles_n, 1);
-  cfg.blockDim = dim3(kSkWarps * 32);
-  cfg.dynamicSmemBytes = kSmem;
-  cfg.stream = s;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = (unsigned)p.split_k;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, k, mw, mx, p, 0);
+  cudaError_t e = launch_pdl(k, dim3((unsigned)p.split_k, (unsigned)p.tiles_n, 1), dim3(kSkWarps * 32), kSmem, s,
+                             (unsigned)p.split_k, mw, mx, p, 0);
   if (e != cudaSuccess) { set_last_error("gemm_tc_skinny cluster launch", e); return FXPR_ERR_CUDA; }
   return check_launch("gemm_tc_skinny");
 }
@@ -279,7 +279,8 @@ static int launch_skinny(const CUtensorMap& mw, const CUtensorMap& mx, TcParams&
   p.tiles_n = (p.N + 127) / 128;
   const int64_t items = (int64_t)p.tiles_n * p.split_k;
   const int grid = (int)(items < sms ? items : sms);
-  k<<<grid, kSkWarps * 32, kSmem, s>>>(mw, mx, p, 0);
+  cudaError_t e = launch_pdl(k, dim3((unsigned)grid), dim3(kSkWarps * 32), kSmem, s, 1u, mw, mx, p, 0);
+  if (e != cudaSuccess) { set_last_error("gemm_tc_skinny launch", e); return FXPR_ERR_CUDA; }
   return check_launch("gemm_tc_skinny");
 }
 

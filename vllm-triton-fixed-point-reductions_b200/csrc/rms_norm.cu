@@ -26,6 +26,8 @@ rms_norm_kernel(const T* __restrict__ x, T* __restrict__ residual, const T* __re
                 T* __restrict__ y, int hidden, float eps, float scale, float inv_scale) {
   extern __shared__ __align__(16) float row_cache[];
   __shared__ long long red[32];
+  pdl_launch_dependents();
+  pdl_wait();
 
   const int64_t base = (int64_t)blockIdx.x * hidden;
   const T* xr = x + base;
@@ -85,6 +87,8 @@ rms_norm_from_int_kernel(const ACC* __restrict__ acc_in, const T* __restrict__ b
                          float scale, float inv_scale) {
   extern __shared__ __align__(16) float row_cache[];
   __shared__ long long red[32];
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t base = (int64_t)blockIdx.x * hidden;
   const ACC* ar = acc_in + base;
   T* rr = residual + base;
@@ -125,8 +129,9 @@ static int launch_rms_from_int(const void* acc, int int_bits, const void* bias, 
       cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxCacheBytes); \
       if (e != cudaSuccess) { set_last_error("rms_norm_from_int smem attribute", e); return FXPR_ERR_CUDA; } \
     }                                                                                                   \
-    k<<<(unsigned)rows, threads, cache_bytes, s>>>((const ACC*)acc, (const T*)bias, (T*)r, (const T*)w, \
-                                                  (T*)y, hidden, eps, gemm_inv, scale, inv);           \
+    cudaError_t le = launch_pdl(k, dim3((unsigned)rows), dim3(threads), cache_bytes, s, 1u, (const ACC*)acc, \
+                                (const T*)bias, (T*)r, (const T*)w, (T*)y, hidden, eps, gemm_inv, scale, inv); \
+    if (le != cudaSuccess) { set_last_error("rms_norm_from_int launch", le); return FXPR_ERR_CUDA; }   \
   } while (0)
   if (int_bits == 64) FXPR_RMS_INT(long long);
   else if (int_bits == 32) FXPR_RMS_INT(int32_t);
@@ -149,11 +154,13 @@ static int launch_rms(const void* x, void* r, const void* w, void* y, int64_t ro
                                            kMaxCacheBytes);
       if (e != cudaSuccess) { set_last_error("rms_norm smem attribute", e); return FXPR_ERR_CUDA; }
     }
-    k<<<(unsigned)rows, threads, cache_bytes, s>>>((const T*)x, (T*)r, (const T*)w, (T*)y, hidden,
-                                                  eps, scale, inv);
+    cudaError_t le = launch_pdl(k, dim3((unsigned)rows), dim3(threads), cache_bytes, s, 1u, (const T*)x, (T*)r,
+                                (const T*)w, (T*)y, hidden, eps, scale, inv);
+    if (le != cudaSuccess) { set_last_error("rms_norm launch", le); return FXPR_ERR_CUDA; }
   } else {
-    rms_norm_kernel<T, VEC, RESIDUAL, false><<<(unsigned)rows, threads, 0, s>>>(
-        (const T*)x, (T*)r, (const T*)w, (T*)y, hidden, eps, scale, inv);
+    cudaError_t le = launch_pdl(rms_norm_kernel<T, VEC, RESIDUAL, false>, dim3((unsigned)rows), dim3(threads), 0, s,
+                                1u, (const T*)x, (T*)r, (const T*)w, (T*)y, hidden, eps, scale, inv);
+    if (le != cudaSuccess) { set_last_error("rms_norm launch", le); return FXPR_ERR_CUDA; }
   }
   return check_launch("rms_norm");
 }

@@ -77,6 +77,8 @@ tp_reduce_norm_kernel(const TpPeers peers, uint32_t* __restrict__ ctl, int world
   __shared__ int s_abort;
   __shared__ int s_last;
 
+  pdl_launch_dependents();
+  pdl_wait();
   // written once per call by the last CTA of the previous launch, after everything else
   const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(ctl) + 1;
   uint32_t* my_flags = peers.flags[rank];
@@ -185,8 +187,10 @@ static int launch_tp(const TpPeers& peers, void* ctl, int world, int rank, int i
       cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024); \
       if (e != cudaSuccess) { set_last_error("tp_reduce_norm smem attribute", e); return FXPR_ERR_CUDA; } \
     }                                                                                                 \
-    k<<<grid, kTpThreads, smem, s>>>(peers, (uint32_t*)ctl, world, rank, (int)rows, rows_per, hidden, \
-                                     (const T*)bias, (const T*)w, eps, gemm_inv, scale, inv, timeout, status); \
+    cudaError_t le = launch_pdl(k, dim3(grid), dim3(kTpThreads), smem, s, 1u, peers, (uint32_t*)ctl, world, rank, \
+                                (int)rows, rows_per, hidden, (const T*)bias, (const T*)w, eps, gemm_inv, scale,  \
+                                inv, timeout, status);                                                \
+    if (le != cudaSuccess) { set_last_error("tp_reduce_norm launch", le); return FXPR_ERR_CUDA; }     \
   } while (0)
   if (int_bits == 64) FXPR_TP_LAUNCH(long long);
   else FXPR_TP_LAUNCH(int32_t);
