@@ -110,6 +110,9 @@ def sample_clocks_under_load(fn, index: int, seconds: float = 1.5):
 def time_cuda(fn, steps: int, warmup: int, dist=None) -> float:
     """Seconds for `steps` calls of fn (device time via CUDA events on the current
     stream), after `warmup` untimed calls; max over ranks."""
+    if dist is not None:
+        dist.barrier()          # sets the communicator up now, so the GPU does not idle (and clock
+        #                         down) between the warm-up and the timed region
     for i in range(warmup):
         fn(i)
     if dist is not None:
@@ -269,6 +272,11 @@ def run_gpu_arm(args):
         outs[i % nsets] = torch.ops.fxpr.gemm_fxp(a, b, None, GEMM["int_bits"], GEMM["frac_bits"])
 
     with L.overrides(gemm_k_tile=GEMM["k_tile"], gemm_split_k=1):
+        # set-up, not warm-up: one pass over every input set, so that each output slot has had
+        # its allocation before anything is timed
+        for i in range(nsets):
+            gemm_step(i)
+        torch.cuda.synchronize()
         # bitwise invariance: split-K sweep and repeats on set 0
         a0, b0 = sets[0]
         ref = torch.ops.fxpr.gemm_fxp(a0, b0, None, 64, 16)
@@ -608,8 +616,15 @@ def bench_others(dev, peaks, L, syn):
         torch.ops.fxpr.unified_attention_fxp(q, kv, o, qsl, sl, bt, max(plens), None, True, None, 64,
                                              16, 0.0, 0, 1)
     sec = t(pstep, steps=3, warm=1)
+    o_tc = o.clone()
+    from fxpr_vllm import _native as nat
+    with L.overrides(attn_flags=nat.ATTN_NO_TCGEN05):
+        sec_mma = t(pstep, steps=3, warm=1)
     res["prefill_attention_cfg3a"] = {"ms": sec * 1e3, "TFLOP/s": fl / sec / 1e12,
-                                      "frac_tensor_measured": fl / sec / 1e12 / peaks["bf16_tflops"]}
+                                      "frac_tensor_measured": fl / sec / 1e12 / peaks["bf16_tflops"],
+                                      "route": "tcgen05 + TMEM + TMA (attn_tc_prefill_kernel)",
+                                      "mma_sync_kernel_ms": sec_mma * 1e3,
+                                      "routes_bit_identical": bool(torch.equal(o_tc, o))}
     L.check_device_status()
     return res
 

@@ -44,6 +44,7 @@ extern "C" {
 #define FXPR_GEMM_NO_CLUSTER     16 /* M <= 64 split-K: partial planes in the scratch instead of a cluster merge (tests) */
 #define FXPR_GEMM_TILE_N256       64 /* force 128 x 256 output tiles (same bits) */
 #define FXPR_GEMM_TILE_N128       128 /* force 128 x 128 output tiles (same bits) */
+#define FXPR_GEMM_SILU_MUL        1024 /* B's columns are (gate_j, up_j) pairs; c is [M, N/2] = silu(gate) * up, computed from the GEMM outputs as the io dtype holds them (same bits as fxpr_gemm + fxpr_silu_mul_pairs); M <= 64 on the tensor-core decode route with c_int == NULL, else FXPR_ERR_UNSUPPORTED */
 #define FXPR_GEMM_PAIR            512 /* two-SM kernel (gemm_tc_pair.cu): 256 x BN tiles on CTA pairs, tcgen05 cta_group::2; same bits, opt-in */
 
 /* ---- attention flags --------------------------------------------------- */
@@ -278,7 +279,8 @@ int fxpr_attention_static_scratch(
  * reshape_and_cache_flash call of fxpr_vllm/attention_backend.py:253-277 plus the RoPE op
  * before it.
  * fxpr_silu_mul: out[r, c] = silu(gate_up[r, c]) * gate_up[r, f + c] for a fused [rows, 2 f]
- * activation (vLLM's SiluAndMul).
+ * activation (vLLM's SiluAndMul).  fxpr_silu_mul_pairs: the same for a [rows, 2 f] activation
+ * whose columns are (gate_j, up_j) pairs, the layout FXPR_GEMM_SILU_MUL expects of its weights.
  */
 int fxpr_rope_kv_write(const void* qkv, int dtype, const float* cos_table, const float* sin_table,
                        const int64_t* positions, const int64_t* seq_ids,
@@ -288,6 +290,8 @@ int fxpr_rope_kv_write(const void* qkv, int dtype, const float* cos_table, const
                        int64_t kv_sslot, int64_t kv_shead, void* stream);
 int fxpr_silu_mul(const void* gate_up, int dtype, void* out, int64_t rows, int64_t f,
                   void* stream);
+int fxpr_silu_mul_pairs(const void* gate_up, int dtype, void* out, int64_t rows, int64_t f,
+                        void* stream);
 
 #ifdef __cplusplus
 }

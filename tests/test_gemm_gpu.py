@@ -357,3 +357,40 @@ def test_two_sm_kernel_agrees_on_random_shapes():
         assert torch.equal(got, exp), (case, M, N, K, kt, split, int_bits, dtype)
         assert torch.equal(got_c.view(torch.int16), exp_c.view(torch.int16)), case
     L.check_device_status()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,f,K", [(64, 1792, 1024), (33, 200, 512), (1, 128, 256), (64, 4096, 2048)])
+@pytest.mark.parametrize("split", [0, 1, 2, 3, 4])
+def test_silu_mul_epilogue_equals_gemm_then_silu_mul(dtype, M, f, K, split):
+    """The decode-shape GEMM with (gate, up) column pairs and SiLU*mul in its epilogue gives the
+    bits of the plain GEMM on [gate | up] followed by the SiLU*mul kernel, for every split
+    route (one CTA per tile, cluster merge, partial planes), and so does the two-kernel form on
+    the paired layout that larger batches take."""
+    from fxpr_vllm import _lib as L
+
+    g = torch.Generator().manual_seed(M * 7 + f)
+    a = torch.randn(M, K, generator=g).to(dtype).cuda()
+    wg = (0.05 * torch.randn(K, f, generator=g)).to(dtype).cuda()
+    wu = (0.05 * torch.randn(K, f, generator=g)).to(dtype).cuda()
+    kw = {} if split == 0 else {"gemm_split_k": split}
+    with L.overrides(gemm_k_tile=128, **kw):
+        want = L.silu_mul(torch.ops.fxpr.gemm_fxp(a, torch.cat([wg, wu], dim=1).contiguous(), None, 64, 16))
+        pairs = L.interleave_gate_up(wg, wu)
+        got = L.gemm_silu_mul(a, pairs, 64, 16)
+        two = L.silu_mul_pairs(torch.ops.fxpr.gemm_fxp(a, pairs, None, 64, 16))
+    assert got.shape == (M, f)
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    assert torch.equal(two.view(torch.int16), want.view(torch.int16))
+
+
+def test_silu_mul_epilogue_falls_back_for_large_batches():
+    from fxpr_vllm import _lib as L
+
+    g = torch.Generator().manual_seed(3)
+    a = torch.randn(200, 512, generator=g).to(torch.bfloat16).cuda()
+    wg = (0.05 * torch.randn(512, 384, generator=g)).to(torch.bfloat16).cuda()
+    wu = (0.05 * torch.randn(512, 384, generator=g)).to(torch.bfloat16).cuda()
+    want = L.silu_mul(torch.ops.fxpr.gemm_fxp(a, torch.cat([wg, wu], dim=1).contiguous(), None, 64, 16))
+    got = L.gemm_silu_mul(a, L.interleave_gate_up(wg, wu), 64, 16)
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))

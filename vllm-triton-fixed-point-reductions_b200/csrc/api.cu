@@ -43,6 +43,10 @@ extern "C" int fxpr_gemm(const void* a, const void* b, const void* bias, void* c
   g.int_bits = int_bits; g.frac_bits = frac_bits; g.k_tile = k_tile; g.split_k = split_k;
   g.scratch = scratch; g.scratch_bytes = scratch_bytes; g.status = status_word; g.flags = flags;
 
+  if (flags & FXPR_GEMM_SILU_MUL) {
+    if (!c || c_int || partials_out || (N & 1)) return FXPR_ERR_BAD_ARG;
+    if ((flags & FXPR_GEMM_FORCE_PORTABLE) || !gemm_tc_supported(g)) return FXPR_ERR_UNSUPPORTED;
+  }
   if (!(flags & FXPR_GEMM_FORCE_PORTABLE) && gemm_tc_supported(g)) return gemm_tc(g, s);
   return gemm_portable(a, b, bias, c, c_int, partials_out, dtype, M, N, K, a_sm, a_sk, b_sk, b_sn,
                        c_sm, int_bits, frac_bits, k_tile, s);

@@ -81,11 +81,22 @@ silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t rows, int
     ActPack<T, VEC> o;
 #pragma unroll
     for (int j = 0; j < VEC; ++j) {
-      const float gf = to_f32<T>(g.v[j]);
-      const float sg = __fdiv_rn(gf, __fadd_rn(1.0f, expf(-gf)));
-      o.v[j] = from_f32<T>(__fmul_rn(sg, to_f32<T>(u.v[j])));
+      o.v[j] = silu_mul_io<T>(to_f32<T>(g.v[j]), to_f32<T>(u.v[j]));
     }
     *reinterpret_cast<ActPack<T, VEC>*>(out + r * f + c) = o;
+  }
+}
+
+// gate and up interleaved by column: gu[r, 2 j] = gate_j, gu[r, 2 j + 1] = up_j
+template <typename T>
+__global__ void __launch_bounds__(256)
+silu_mul_pairs_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t rows, int64_t f) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t n = rows * f;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (int64_t)gridDim.x * blockDim.x) {
+    const ActPack<T, 2> p = *reinterpret_cast<const ActPack<T, 2>*>(gu + 2 * idx);
+    out[idx] = silu_mul_io<T>(to_f32<T>(p.v[0]), to_f32<T>(p.v[1]));
   }
 }
 
@@ -147,4 +158,25 @@ extern "C" int fxpr_silu_mul(const void* gate_up, int dtype, void* out, int64_t 
     default: return FXPR_ERR_UNSUPPORTED;
   }
   return check_launch("silu_mul");
+}
+
+extern "C" int fxpr_silu_mul_pairs(const void* gate_up, int dtype, void* out, int64_t rows, int64_t f,
+                                   void* stream) {
+  if (rows < 0 || f < 0) return FXPR_ERR_BAD_ARG;
+  if (rows == 0 || f == 0) return FXPR_OK;
+  if (!gate_up || !out) return FXPR_ERR_BAD_ARG;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int64_t n = rows * f;
+  const unsigned grid = (unsigned)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+#define FXPR_SILU_PAIRS(TT)                                                                         \
+  (void)launch_pdl(silu_mul_pairs_kernel<TT>, dim3(grid), dim3(256), 0, s, 1u, (const TT*)gate_up,  \
+                   (TT*)out, rows, f)
+  switch (dtype) {
+    case FXPR_BF16: FXPR_SILU_PAIRS(__nv_bfloat16); break;
+    case FXPR_F16: FXPR_SILU_PAIRS(__half); break;
+    case FXPR_F32: FXPR_SILU_PAIRS(float); break;
+    default: return FXPR_ERR_UNSUPPORTED;
+  }
+#undef FXPR_SILU_PAIRS
+  return check_launch("silu_mul_pairs");
 }

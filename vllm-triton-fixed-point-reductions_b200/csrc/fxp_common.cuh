@@ -143,6 +143,14 @@ template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 template <> __device__ __forceinline__ double from_f32<double>(float v) { return (double)v; }
 
+// silu(g) * u on values the io dtype holds, rounded back to it (the SiLU*mul kernels and the
+// GEMM epilogue that fuses them share this, so their bits agree)
+template <typename T>
+__device__ __forceinline__ T silu_mul_io(float g, float u) {
+  const float sg = __fdiv_rn(g, __fadd_rn(1.0f, expf(-g)));
+  return from_f32<T>(__fmul_rn(sg, u));
+}
+
 // ---- deterministic 2^t -----------------------------------------------------------
 // n = rint(t), f = t - n (exact), degree-7 Horner polynomial of 2^f with separate
 // multiply and add, exact scaling by 2^n.  t < -125 or NaN -> 0; t > 127 -> +inf.

@@ -454,6 +454,7 @@ int gemm_tc(const GemmArgs& g, cudaStream_t s) {
   p.idesc = make_idesc(g.dtype == FXPR_BF16 ? 1 : 0, b_kmajor ? 0 : 1, BN, kBM);
   p.c_vec_ok = (g.c && (((uintptr_t)g.c & 15) == 0) && (g.c_sm % 8 == 0)) ? 1 : 0;
   p.status = g.status;
+  p.silu_mul = 0;
   const int k_tiles = (int)((g.K + g.k_tile - 1) / g.k_tile);
   p.split_k = g.split_k < 1 ? 1 : (g.split_k > k_tiles ? k_tiles : g.split_k);
   p.acc_scratch = nullptr; p.locks = nullptr;
@@ -467,8 +468,11 @@ int gemm_tc(const GemmArgs& g, cudaStream_t s) {
   }
 
   // decode shapes: weights on the 128-row side of the MMA (same bits, see gemm_tc_skinny.cu)
-  if (!(g.flags & (FXPR_GEMM_FORCE_EXACT_TC | FXPR_GEMM_NO_SKINNY)) && gemm_tc_skinny_supported(g, p.split_k))
+  if (!(g.flags & (FXPR_GEMM_FORCE_EXACT_TC | FXPR_GEMM_NO_SKINNY)) && gemm_tc_skinny_supported(g, p.split_k)) {
+    p.silu_mul = (g.flags & FXPR_GEMM_SILU_MUL) ? 1 : 0;
     return gemm_tc_skinny(g, p, mb, s);
+  }
+  if (g.flags & FXPR_GEMM_SILU_MUL) return FXPR_ERR_UNSUPPORTED;   // only the decode-shape kernel fuses it
   // 128 x 256 tiles: measured +6 % at k_tile 128 (two 64-deep stages per accumulator) and -12 %
   // at k_tile 64 (one MMA group per hand-off with only two accumulators in TMEM), same bits;
   // so they are the default for k_tile 128 only.  The flags force either shape.

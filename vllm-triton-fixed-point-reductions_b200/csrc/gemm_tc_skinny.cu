@@ -199,10 +199,22 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_co
       const T* bias = (const T*)p.bias;
       for (int idx = (int)threadIdx.x - 64; idx < rows_per * 128; idx += EPIW * 32) {
         const int m = mr0 + idx / 128, nl = idx % 128, n = tile * 128 + nl;
-        if (m >= p.M || n >= p.N) continue;
+        const bool live = m < p.M && n < p.N;
         long long q = 0;
-        for (int rr = 0; rr < S; ++rr) q += cluster.map_shared_rank(red, rr)[m * 128 + nl];
+        if (live)
+          for (int rr = 0; rr < S; ++rr) q += cluster.map_shared_rank(red, rr)[m * 128 + nl];
         if (p.int_bits != 64) q = (long long)(int32_t)q;
+        if (p.silu_mul) {
+          // (gate, up) column pairs sit in neighbouring lanes (idx runs with the lane)
+          float v = fixed_to_float<long long>(q, p.inv_scale);
+          if (bias && live) v = __fadd_rn(v, to_f32<T>(bias[n]));
+          const float mine = to_f32<T>(from_f32<T>(v));
+          const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
+          if (live && !(nl & 1) && n + 1 < p.N)
+            ((T*)p.c)[(int64_t)m * p.c_sm + (n >> 1)] = silu_mul_io<T>(mine, other);
+          continue;
+        }
+        if (!live) continue;
         if (p.c_int) {
           if (p.int_bits == 64) ((long long*)p.c_int)[(int64_t)m * p.N + n] = q;
           else ((int32_t*)p.c_int)[(int64_t)m * p.N + n] = (int32_t)q;

@@ -144,7 +144,22 @@
           for (int i = 0; i < kCols; ++i) q[i] = (long long)(int32_t)q[i];
         }
       }
-      if (n < p.N) {
+      if (p.silu_mul) {
+        // columns come in (gate, up) pairs held by neighbouring lanes: the even lane combines the
+        // two outputs as the io dtype holds them and writes column n / 2 of the [M, N / 2] result
+        const T* bias = (const T*)p.bias;
+        const float bias_f = (bias && n < p.N) ? to_f32<T>(bias[n]) : 0.0f;
+#pragma unroll
+        for (int i = 0; i < kCols; ++i) {
+          float v = fixed_to_float<long long>(q[i], p.inv_scale);
+          if (bias) v = __fadd_rn(v, bias_f);
+          const float mine = to_f32<T>(from_f32<T>(v));
+          const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
+          const int m = m0 + i;
+          if (!(lane & 1) && n + 1 < p.N && m < p.M)
+            ((T*)p.c)[(int64_t)m * p.c_sm + (n >> 1)] = silu_mul_io<T>(mine, other);
+        }
+      } else if (n < p.N) {
         const T* bias = (const T*)p.bias;
         const float bias_f = bias ? to_f32<T>(bias[n]) : 0.0f;
 #pragma unroll

@@ -149,6 +149,7 @@ struct TcParams {
   int M, N, K; int64_t c_sm;
   int k_tile, split_k, int_bits; float scale, inv_scale;
   int tiles_m, tiles_n; uint32_t idesc; int b_kmajor; int c_vec_ok;
+  int silu_mul;          // decode-shape kernel only: c[m, n / 2] = silu(out[m, n]) * out[m, n + 1], n even
 };
 
 template <int BN, int STAGES>

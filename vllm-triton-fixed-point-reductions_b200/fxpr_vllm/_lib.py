@@ -413,10 +413,11 @@ def pick_split_k(M: int, N: int, K: int, k_tile: int, int_bits: int, num_sms: in
     return split
 
 
-def _gemm_common(a, b, bias, int_bits, frac_bits, want_c: bool, want_int: bool, out_int=None):
+def _gemm_common(a, b, bias, int_bits, frac_bits, want_c: bool, want_int: bool, out_int=None,
+                 silu_pairs: bool = False):
     M, K = a.shape
     N = b.shape[1]
-    c = torch.empty((M, N), device=a.device, dtype=a.dtype) if want_c else None
+    c = torch.empty((M, N // 2 if silu_pairs else N), device=a.device, dtype=a.dtype) if want_c else None
     if out_int is not None:
         if (out_int.shape != (M, N) or out_int.dtype != _INT_DTYPE[int_bits] or not out_int.is_contiguous()
                 or out_int.device != a.device):
@@ -437,6 +438,8 @@ def _gemm_common(a, b, bias, int_bits, frac_bits, want_c: bool, want_int: bool, 
         split_k = pick_split_k(M, N, K, k_tile, int_bits, _sm_count(a.device))
     split_k = max(1, min(split_k, -(-K // k_tile) if K else 1))
     flags = (nat.GEMM_FORCE_PORTABLE if _ovr.gemm_portable else 0) | int(_ovr.gemm_flags)
+    if silu_pairs:
+        flags |= nat.GEMM_SILU_MUL
     lib = nat.load()
     scratch = None
     scratch_bytes = 0
@@ -457,6 +460,8 @@ def _gemm_common(a, b, bias, int_bits, frac_bits, want_c: bool, want_int: bool, 
             c.stride(0) if c is not None else N, int_bits, frac_bits, k_tile, split_k, flags,
             nat.ptr(scratch), scratch_bytes, nat.ptr(partials if partials is not None and partials.numel() else None),
             _status_word(a.device).data_ptr(), nat.stream_ptr(a.device))
+    if silu_pairs and st == nat.FXPR_ERR_UNSUPPORTED:
+        return None, None                       # the caller runs the two-kernel form
     nat.check(st, "gemm_fxp")
     return c, c_int
 
@@ -470,6 +475,41 @@ def gemm_fxp_run(a, b, bias, int_bits, fxp_frac_bits):
 def gemm_fxp_int_run(a, b, int_bits, fxp_frac_bits):
     _, c_int = _gemm_common(a, b, None, int_bits, fxp_frac_bits, False, True)
     return c_int
+
+
+def silu_mul_pairs(gate_up):
+    """``silu(gate_up[:, 0::2]) * gate_up[:, 1::2]`` for an activation whose columns are
+    (gate_j, up_j) pairs (the layout ``gemm_silu_mul`` keeps its weights in)."""
+    if gate_up.dtype not in _IO_DTYPES or gate_up.dim() != 2 or gate_up.shape[1] % 2:
+        raise TypeError("silu_mul_pairs: [rows, 2f] tensor of an io dtype expected")
+    gate_up = gate_up.contiguous()
+    rows, f = gate_up.shape[0], gate_up.shape[1] // 2
+    out = torch.empty((rows, f), device=gate_up.device, dtype=gate_up.dtype)
+    if rows and f:
+        with _on_device(gate_up):
+            st = nat.load().fxpr_silu_mul_pairs(gate_up.data_ptr(), nat.DTYPE_CODE[gate_up.dtype],
+                                                out.data_ptr(), rows, f, nat.stream_ptr(gate_up.device))
+        nat.check(st, "silu_mul_pairs")
+    return out
+
+
+def interleave_gate_up(w_gate, w_up):
+    """``(K, f)`` gate and up weights -> ``(K, 2f)`` with columns (gate_0, up_0, gate_1, ...)."""
+    return torch.stack([w_gate, w_up], dim=2).reshape(w_gate.shape[0], -1).contiguous()
+
+
+def gemm_silu_mul(a, b_pairs, int_bits, fxp_frac_bits):
+    """``silu(a @ gate) * (a @ up)`` with the gate and up columns of ``b_pairs`` interleaved
+    (``interleave_gate_up``).  For at most 64 rows the decode-shape GEMM combines the column pairs
+    in its epilogue; otherwise the GEMM and ``silu_mul_pairs`` run one after the other.  Same bits
+    either way (and as ``gemm_fxp`` + ``silu_mul`` on the plain layout)."""
+    if b_pairs.shape[1] % 2:
+        raise ValueError("gemm_silu_mul: the weight needs an even number of columns")
+    if a.shape[0] <= 64:
+        c, _ = _gemm_common(a, b_pairs, None, int_bits, fxp_frac_bits, True, False, silu_pairs=True)
+        if c is not None:
+            return c
+    return silu_mul_pairs(gemm_fxp_run(a, b_pairs, None, int_bits, fxp_frac_bits))
 
 
 def gemm_fxp_int_into(a, b, out, int_bits, fxp_frac_bits):

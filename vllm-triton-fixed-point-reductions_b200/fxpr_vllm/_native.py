@@ -47,6 +47,7 @@ GEMM_FORCE_EXACT_TC = 2
 GEMM_NO_SKINNY = 8
 GEMM_NO_CLUSTER = 16
 GEMM_PAIR = 512
+GEMM_SILU_MUL = 1024
 GEMM_TILE_N256 = 64
 GEMM_TILE_N128 = 128
 ATTN_CAUSAL = 1
@@ -77,6 +78,7 @@ SIGNATURES = {
     "fxpr_rope_kv_write": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _i64, _i, _i, _i, _i,
                                 _i64, _i64, _i64, _i64, _vp]),
     "fxpr_silu_mul": (_i, [_vp, _i, _vp, _i64, _i64, _vp]),
+    "fxpr_silu_mul_pairs": (_i, [_vp, _i, _vp, _i64, _i64, _vp]),
     "fxpr_gemm_scratch_bytes": (_i64, [_i64, _i64, _i, _i]),
     "fxpr_gemm": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i64, _i64, _i64,
                        _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i,

@@ -19,13 +19,15 @@ the same bits), then one fixed->float epilogue runs on every rank.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 
 import torch
 import torch.distributed as dist
 
 from . import library_ops as ops
-from ._lib import BLOCK_K_BY_DTYPE, gemm_fxp_int_into, rope_kv_write, silu_mul
+from ._lib import (BLOCK_K_BY_DTYPE, gemm_fxp_int_into, gemm_silu_mul, interleave_gate_up, rope_kv_write,
+                   silu_mul_pairs)
 from .config import get_runtime_config
 from .tp import check_shardable
 
@@ -114,6 +116,9 @@ class LlamaDecoder:
         self.cfg, self.group, self.device = cfg, group, torch.device(device)
         # fused CUDA kernels for RoPE + KV-cache write and SiLU*mul, or the same steps as torch ops
         self.fused = fused_elementwise
+        # SiLU*mul inside the gate/up GEMM's epilogue for decode-sized batches (same bits as the
+        # separate kernel); FXPR_DECODER_SILU_KERNEL=1 keeps the separate kernel (A/B timing)
+        self.silu_epilogue = os.environ.get("FXPR_DECODER_SILU_KERNEL") != "1"
         tp = group.size
         if cfg.q_heads % tp or cfg.kv_heads % tp or cfg.ffn % tp or cfg.vocab % tp:
             raise ValueError(f"tp={tp} does not divide the head / ffn / vocab sizes")
@@ -144,8 +149,13 @@ class LlamaDecoder:
                 sh.qkv.append(torch.cat([wq[:, q0:q0 + self.qh * hd], wk[:, k0:k0 + self.kvh * hd],
                                          wv[:, k0:k0 + self.kvh * hd]], dim=1).contiguous())
                 sh.o.append(wo[q0:q0 + self.qh * hd].contiguous())
-                sh.gate_up.append(torch.cat([wg[:, f0:f0 + cfg.ffn // tp],
-                                             wu[:, f0:f0 + cfg.ffn // tp]], dim=1).contiguous())
+                if self.fused:
+                    # (gate_j, up_j) column pairs: the decode-shape GEMM applies SiLU*mul in its epilogue
+                    sh.gate_up.append(interleave_gate_up(wg[:, f0:f0 + cfg.ffn // tp],
+                                                         wu[:, f0:f0 + cfg.ffn // tp]))
+                else:
+                    sh.gate_up.append(torch.cat([wg[:, f0:f0 + cfg.ffn // tp],
+                                                 wu[:, f0:f0 + cfg.ffn // tp]], dim=1).contiguous())
                 sh.down.append(wd[f0:f0 + cfg.ffn // tp].contiguous())
                 sh.kv_cache.append(torch.zeros((max_seqs * self.blocks_per_seq + 1, 2, cfg.page,
                                                 self.kvh, hd), device=dev, dtype=dt))
@@ -241,10 +251,12 @@ class LlamaDecoder:
             h = self._row_parallel_norm(outs, [sh.o[layer] for sh in shards], residual, self.norm_w[2 * layer + 1])
             acts = []
             for sh in shards:
-                gu = ops.gemm_fxp(h, sh.gate_up[layer], None, c.int_bits, c.frac_bits)
-                if self.fused:
-                    acts.append(silu_mul(gu))
+                if self.fused and self.silu_epilogue:
+                    acts.append(gemm_silu_mul(h, sh.gate_up[layer], c.int_bits, c.frac_bits))
+                elif self.fused:
+                    acts.append(silu_mul_pairs(ops.gemm_fxp(h, sh.gate_up[layer], None, c.int_bits, c.frac_bits)))
                 else:
+                    gu = ops.gemm_fxp(h, sh.gate_up[layer], None, c.int_bits, c.frac_bits)
                     f = gu.shape[1] // 2
                     acts.append((torch.nn.functional.silu(gu[:, :f].float()) * gu[:, f:].float()).to(c.dtype))
             # the norm in front of the next layer (or, after the last layer, the final norm)
