@@ -194,12 +194,12 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_co
     if (warp >= 2 && !*abort_flag) {
       const int S = p.split_k, rank = (int)blockIdx.x;
       const long long* red = reinterpret_cast<const long long*>(smem_gen);
-      const int rows_per = MP / S, mr0 = rank * rows_per;
+      const int rows_per = (MP + S - 1) / S, mr0 = rank * rows_per;   // any S <= 8; the last rank may get fewer
       const int tile = (int)blockIdx.y;
       const T* bias = (const T*)p.bias;
       for (int idx = (int)threadIdx.x - 64; idx < rows_per * 128; idx += EPIW * 32) {
         const int m = mr0 + idx / 128, nl = idx % 128, n = tile * 128 + nl;
-        const bool live = m < p.M && n < p.N;
+        const bool live = m < MP && m < p.M && n < p.N;
         long long q = 0;
         if (live)
           for (int rr = 0; rr < S; ++rr) q += cluster.map_shared_rank(red, rr)[m * 128 + nl];
@@ -307,9 +307,9 @@ int gemm_tc_skinny(const GemmArgs& g, TcParams& p, const CUtensorMap& mw, cudaSt
   }
   // M = 128 weight columns, N = 64 activation rows; bit 15: the 128-row operand is MN-major
   p.idesc = make_idesc(g.dtype == FXPR_BF16 ? 1 : 0, 0, kSkMP, 128) | (p.b_kmajor ? 0u : (1u << 15));
-  // 2, 4 or 8 splits run as a thread-block cluster (merge through distributed shared memory);
-  // other split counts use the partial planes in the caller's scratch.  Same bits either way.
-  const bool cluster = (p.split_k == 2 || p.split_k == 4 || p.split_k == 8) && (p.N + 127) / 128 <= 65535 &&
+  // 2 to 8 splits run as a thread-block cluster (merge through distributed shared memory);
+  // larger split counts use the partial planes in the caller's scratch.  Same bits either way.
+  const bool cluster = p.split_k >= 2 && p.split_k <= 8 && (p.N + 127) / 128 <= 65535 &&
                        !(g.flags & FXPR_GEMM_NO_CLUSTER);
   if (cluster) {
     if (g.dtype == FXPR_BF16) return launch_skinny_cluster<__nv_bfloat16>(mw, mx, p, s);

@@ -406,6 +406,14 @@ def pick_split_k(M: int, N: int, K: int, k_tile: int, int_bits: int, num_sms: in
     k_tiles = -(-K // k_tile)
     if tiles_mn >= num_sms or k_tiles < 8:
         return 1
+    if M <= 64:
+        # decode shapes (cluster merge): the largest power of two that fills the SMs once --
+        # clusters of CTAs that each take a whole SM do not pack the last tenth of the SMs --
+        # and leaves every rank at least 384 of K (below that the fixed cost of a rank wins)
+        split = 1
+        while split < 8 and tiles_mn * split * 2 <= num_sms * 9 // 10 and K // (split * 2) >= 384:
+            split *= 2
+        return split
     split = 1
     # one wave of CTAs at most: a second, partly filled wave costs more than it hides
     while split < 16 and tiles_mn * split * 2 <= num_sms and k_tiles // (split * 2) >= 4:
@@ -584,13 +592,26 @@ def pick_num_splits_b200(requested, num_requests, max_query_len, num_heads, num_
                          max_keys, num_sms):
     """Split policy of the tensor-core route, where splits are cluster ranks: results do
     not depend on it, so it only balances the GPU.  Decode keeps each CTA's key slice near
-    1024 keys (small score stash -> more resident CTAs); prefill splits only when the row
+    1024 keys (small score stash -> more resident CTAs) unless fewer clusters than CTA slots call for more ranks; prefill splits only when the row
     blocks alone cannot fill the SMs.  Host shapes only, so it is fixed under a CUDA graph."""
     if requested >= 1:
         return min(requested, 16)
     g = num_heads // num_kv_heads
     if max_query_len * g <= 16:
-        return max(1, min(8, -(-max_keys // 1024)))
+        # A rank's score stash must leave room for four CTAs per SM (about 19.5 KB: 19 key tiles
+        # at 16 bytes per key), which sets the least rank count for long contexts.  Few clusters:
+        # enough ranks to fill one wave of 4 CTAs per SM, at least two key tiles each.  Measured
+        # on 64 requests x 1152 keys: 8 KV heads 70 -> 63 us with 1 rank instead of 2 (when the
+        # block table is no wider than that), 2 KV heads 30 -> 20.5 us with 4, 1 KV head 25 -> 16 us
+        # with 8.
+        tiles = -(-max_keys // 64)
+        key_bytes = 4 * g if g <= 8 else 64
+        cap_tiles = max(1, (19968 // key_bytes) // 64)
+        by_keys = -(-tiles // cap_tiles)
+        by_keys = 8 if by_keys > 4 else max(1, by_keys)
+        clusters = max(1, num_requests * num_kv_heads)
+        by_fill = max(1, min(8, (4 * num_sms) // clusters, tiles // 2))
+        return max(by_keys, by_fill)
     rows_per_block = 64
     blocks = num_requests * num_kv_heads * max(1, -(-(max_query_len * g) // rows_per_block))
     if blocks >= num_sms or max_keys <= 2048:
