@@ -430,7 +430,8 @@ def bench_llama(dev, dist, world, peaks, batch=64, prompt_len=1024, gen=256):
 
         def decode_all_graph():
             for _ in range(gen):
-                state["logits"] = model.replay_decode()
+                model.replay_decode()
+            state["logits"] = model.last_logits()
 
         _, decode_ms = timed(decode_all_graph)
         state["tok"] = model._g_tok
@@ -481,7 +482,7 @@ def _tp_scaling(model, cfg, dev, dist, world, timed, state, prompts, prompt_len,
                 model.replay_decode()
 
         _, ms = timed(replay)
-        return ms / short, _digest(model._g_logits)
+        return ms / short, _digest(model.last_logits())
 
     peer, model.peer = model.peer, None
     nccl_ms, d_nccl = run()

@@ -269,6 +269,21 @@ int fxpr_attention_static_scratch(
                    int32_t* status_word, void* stream);
 
 /*
+ * fxpr_gemm for at most 64 rows that also leaves, per row, the arg-max of the outputs (greedy
+ * sampling straight from the lm_head without a pass over the logits; no reference counterpart):
+ * best[m] (zeroed by the call) becomes the maximum over columns n of the key
+ * (order-preserving bits of c[m, n] as the io dtype holds it) << 32 | (0xFFFFFFFF - (n_offset + n)),
+ * so the winning column is 0xFFFFFFFF - (best[m] & 0xFFFFFFFF): the largest output, the
+ * smallest column among equals (torch.argmax's rule).  Keys of column shards (vocab-parallel
+ * lm_head: n_offset = first column of the shard) combine by a plain integer maximum.  c is
+ * still written.  Tensor-core decode route only (split_k 1), else FXPR_ERR_UNSUPPORTED.
+ */
+int fxpr_gemm_argmax(const void* a, const void* b, const void* bias, void* c, uint64_t* best,
+                     int64_t n_offset, int dtype, int64_t M, int64_t N, int64_t K, int64_t a_sm,
+                     int64_t a_sk, int64_t b_sk, int64_t b_sn, int64_t c_sm, int int_bits,
+                     int frac_bits, int k_tile, int flags, int32_t* status_word, void* stream);
+
+/*
  * Decoder-layer element-wise steps around the attention call (no reductions).
  *
  * fxpr_rope_kv_write: qkv is [tokens, (q_heads + 2 kv_heads) * head_dim] (Q heads, K heads,

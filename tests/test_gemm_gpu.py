@@ -394,3 +394,32 @@ def test_silu_mul_epilogue_falls_back_for_large_batches():
     want = L.silu_mul(torch.ops.fxpr.gemm_fxp(a, torch.cat([wg, wu], dim=1).contiguous(), None, 64, 16))
     got = L.gemm_silu_mul(a, L.interleave_gate_up(wg, wu), 64, 16)
     assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,N,K", [(64, 16032, 512), (33, 1000, 256), (1, 128, 128), (64, 4096, 1024)])
+def test_gemm_argmax_keys_equal_argmax_of_the_logits(dtype, M, N, K):
+    """The lm_head GEMM that also leaves per-row arg-max keys: same logits as ``gemm_fxp``, the
+    winning column equals ``torch.argmax`` of them (first maximal column: the weights hold
+    duplicated columns, so every row has ties), and the keys of two column shards combine to the
+    key of the whole row."""
+    from fxpr_vllm import _lib as L
+
+    g = torch.Generator().manual_seed(N + M)
+    a = torch.randn(M, K, generator=g).to(dtype).cuda()
+    b = (0.05 * torch.randn(K, N, generator=g)).to(dtype)
+    b[:, N // 3] = b[:, N // 2]                      # exact ties between far-apart columns
+    b[:, N - 1] = b[:, 0]
+    b = b.cuda()
+    want = torch.ops.fxpr.gemm_fxp(a, b, None, 64, 16)
+    logits, keys = L.gemm_fxp_argmax(a, b, None, 64, 16)
+    assert torch.equal(logits.view(torch.int16), want.view(torch.int16))
+    assert torch.equal(L.argmax_from_keys(keys), want.argmax(dim=-1))
+    assert torch.equal(keys, L.argmax_keys_of(want))
+    half = (N // 2 + 127) // 128 * 128 if N > 256 else N // 2
+    k0 = L.gemm_fxp_argmax(a, b[:, :half].contiguous(), None, 64, 16, n_offset=0)[1]
+    k1 = L.gemm_fxp_argmax(a, b[:, half:].contiguous(), None, 64, 16, n_offset=half)[1]
+    assert torch.equal(L.combine_argmax_keys([k0, k1]), keys)
+    big = torch.randn(100, K, generator=g).to(dtype).cuda()      # more than 64 rows: two-kernel form
+    lg2, k2 = L.gemm_fxp_argmax(big, b, None, 64, 16)
+    assert torch.equal(L.argmax_from_keys(k2), lg2.argmax(dim=-1))

@@ -19,11 +19,12 @@ extern "C" int64_t fxpr_gemm_scratch_bytes(int64_t M, int64_t N, int int_bits, i
   return gemm_tc_scratch_bytes(M, N, int_bits, split_k);
 }
 
-extern "C" int fxpr_gemm(const void* a, const void* b, const void* bias, void* c, void* c_int,
-                         int dtype, int64_t M, int64_t N, int64_t K, int64_t a_sm, int64_t a_sk,
-                         int64_t b_sk, int64_t b_sn, int64_t c_sm, int int_bits, int frac_bits,
-                         int k_tile, int split_k, int flags, void* scratch, int64_t scratch_bytes,
-                         float* partials_out, int32_t* status_word, void* stream) {
+static int gemm_entry(const void* a, const void* b, const void* bias, void* c, void* c_int,
+                      int dtype, int64_t M, int64_t N, int64_t K, int64_t a_sm, int64_t a_sk,
+                      int64_t b_sk, int64_t b_sn, int64_t c_sm, int int_bits, int frac_bits,
+                      int k_tile, int split_k, int flags, void* scratch, int64_t scratch_bytes,
+                      float* partials_out, int32_t* status_word, void* stream,
+                      unsigned long long* best, int64_t n_offset) {
   if (M < 0 || N < 0 || K < 0) return FXPR_ERR_BAD_ARG;
   if (int_bits != 16 && int_bits != 32 && int_bits != 64) return FXPR_ERR_BAD_ARG;
   if (frac_bits < 0 || frac_bits >= 63) return FXPR_ERR_BAD_ARG;
@@ -42,7 +43,14 @@ extern "C" int fxpr_gemm(const void* a, const void* b, const void* bias, void* c
   g.a_sm = a_sm; g.a_sk = a_sk; g.b_sk = b_sk; g.b_sn = b_sn; g.c_sm = c_sm;
   g.int_bits = int_bits; g.frac_bits = frac_bits; g.k_tile = k_tile; g.split_k = split_k;
   g.scratch = scratch; g.scratch_bytes = scratch_bytes; g.status = status_word; g.flags = flags;
+  g.best = best; g.n_offset = n_offset;
 
+  if (best) {
+    if (!c || c_int || partials_out || n_offset < 0 || n_offset + N > 0xffffffffLL) return FXPR_ERR_BAD_ARG;
+    if ((flags & FXPR_GEMM_FORCE_PORTABLE) || !gemm_tc_supported(g)) return FXPR_ERR_UNSUPPORTED;
+    cudaError_t e = cudaMemsetAsync(best, 0, (size_t)M * sizeof(unsigned long long), s);
+    if (e != cudaSuccess) { set_last_error("gemm_argmax memset", e); return FXPR_ERR_CUDA; }
+  }
   if (flags & FXPR_GEMM_SILU_MUL) {
     if (!c || c_int || partials_out || (N & 1)) return FXPR_ERR_BAD_ARG;
     if ((flags & FXPR_GEMM_FORCE_PORTABLE) || !gemm_tc_supported(g)) return FXPR_ERR_UNSUPPORTED;
@@ -50,6 +58,27 @@ extern "C" int fxpr_gemm(const void* a, const void* b, const void* bias, void* c
   if (!(flags & FXPR_GEMM_FORCE_PORTABLE) && gemm_tc_supported(g)) return gemm_tc(g, s);
   return gemm_portable(a, b, bias, c, c_int, partials_out, dtype, M, N, K, a_sm, a_sk, b_sk, b_sn,
                        c_sm, int_bits, frac_bits, k_tile, s);
+}
+
+extern "C" int fxpr_gemm(const void* a, const void* b, const void* bias, void* c, void* c_int,
+                         int dtype, int64_t M, int64_t N, int64_t K, int64_t a_sm, int64_t a_sk,
+                         int64_t b_sk, int64_t b_sn, int64_t c_sm, int int_bits, int frac_bits,
+                         int k_tile, int split_k, int flags, void* scratch, int64_t scratch_bytes,
+                         float* partials_out, int32_t* status_word, void* stream) {
+  return gemm_entry(a, b, bias, c, c_int, dtype, M, N, K, a_sm, a_sk, b_sk, b_sn, c_sm, int_bits, frac_bits,
+                    k_tile, split_k, flags, scratch, scratch_bytes, partials_out, status_word, stream,
+                    nullptr, 0);
+}
+
+extern "C" int fxpr_gemm_argmax(const void* a, const void* b, const void* bias, void* c, uint64_t* best,
+                                int64_t n_offset, int dtype, int64_t M, int64_t N, int64_t K,
+                                int64_t a_sm, int64_t a_sk, int64_t b_sk, int64_t b_sn, int64_t c_sm,
+                                int int_bits, int frac_bits, int k_tile, int flags, int32_t* status_word,
+                                void* stream) {
+  if (!best) return FXPR_ERR_BAD_ARG;
+  return gemm_entry(a, b, bias, c, nullptr, dtype, M, N, K, a_sm, a_sk, b_sk, b_sn, c_sm, int_bits, frac_bits,
+                    k_tile, 1, flags, nullptr, 0, nullptr, status_word, stream,
+                    reinterpret_cast<unsigned long long*>(best), n_offset);
 }
 
 extern "C" int64_t fxpr_attention_scratch_bytes(int64_t total_q_tokens, int num_heads, int head_dim,

@@ -11,6 +11,8 @@ struct GemmArgs {
   int dtype; int64_t M, N, K; int64_t a_sm, a_sk, b_sk, b_sn, c_sm;
   int int_bits, frac_bits, k_tile, split_k;
   void* scratch; int64_t scratch_bytes; int32_t* status; int flags;
+  unsigned long long* best = nullptr;   // fxpr_gemm_argmax: per-row (value, column) keys, see tc_common.cuh
+  int64_t n_offset = 0;
 };
 
 // Tensor-core (tcgen05 / TMEM / TMA) kernel.

@@ -455,6 +455,7 @@ int gemm_tc(const GemmArgs& g, cudaStream_t s) {
   p.c_vec_ok = (g.c && (((uintptr_t)g.c & 15) == 0) && (g.c_sm % 8 == 0)) ? 1 : 0;
   p.status = g.status;
   p.silu_mul = 0;
+  p.best = nullptr; p.n_offset = 0;
   const int k_tiles = (int)((g.K + g.k_tile - 1) / g.k_tile);
   p.split_k = g.split_k < 1 ? 1 : (g.split_k > k_tiles ? k_tiles : g.split_k);
   p.acc_scratch = nullptr; p.locks = nullptr;
@@ -470,8 +471,13 @@ int gemm_tc(const GemmArgs& g, cudaStream_t s) {
   // decode shapes: weights on the 128-row side of the MMA (same bits, see gemm_tc_skinny.cu)
   if (!(g.flags & (FXPR_GEMM_FORCE_EXACT_TC | FXPR_GEMM_NO_SKINNY)) && gemm_tc_skinny_supported(g, p.split_k)) {
     p.silu_mul = (g.flags & FXPR_GEMM_SILU_MUL) ? 1 : 0;
+    if (g.best) {
+      if (p.split_k != 1 || p.silu_mul) return FXPR_ERR_UNSUPPORTED;
+      p.best = g.best; p.n_offset = (unsigned int)g.n_offset;
+    }
     return gemm_tc_skinny(g, p, mb, s);
   }
+  if (g.best) return FXPR_ERR_UNSUPPORTED;                          // only the decode-shape kernel
   if (g.flags & FXPR_GEMM_SILU_MUL) return FXPR_ERR_UNSUPPORTED;   // only the decode-shape kernel fuses it
   // 128 x 256 tiles: measured +6 % at k_tile 128 (two 64-deep stages per accumulator) and -12 %
   // at k_tile 64 (one MMA group per hand-off with only two accumulators in TMEM), same bits;

@@ -177,6 +177,41 @@
           }
         }
       }
+      if (p.best) {
+        // Greedy sampling without a pass over the logits: per row, the best (value, column) key
+        // over this warp's 32 columns by recursive halving -- after the exchange with the lane at
+        // distance d a lane keeps half of the rows it held -- then one atomic maximum per row.
+        const T* bias = (const T*)p.bias;
+        const float bias_f = (bias && n < p.N) ? to_f32<T>(bias[n]) : 0.0f;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          unsigned long long key[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            float v = fixed_to_float<long long>(q[half * 16 + i], p.inv_scale);
+            if (bias) v = __fadd_rn(v, bias_f);
+            v = to_f32<T>(from_f32<T>(v));                       // the logit as the io dtype holds it
+            key[i] = n < p.N ? argmax_key(v, p.n_offset + (unsigned int)n) : 0ull;
+          }
+#pragma unroll
+          for (int step = 0; step < 4; ++step) {
+            const int d = 16 >> step, cnt = 8 >> step;
+            const bool upper = (lane & d) != 0;                  // keeps rows [cnt, 2 cnt) of what it holds
+#pragma unroll
+            for (int i = 0; i < cnt; ++i) {
+              const unsigned long long send = upper ? key[i] : key[cnt + i];
+              const unsigned long long recv = __shfl_xor_sync(0xffffffffu, send, d);
+              const unsigned long long mine = upper ? key[cnt + i] : key[i];
+              key[i] = mine > recv ? mine : recv;
+            }
+          }
+          const unsigned long long other = __shfl_xor_sync(0xffffffffu, key[0], 1);
+          const unsigned long long top = key[0] > other ? key[0] : other;
+          const int row = half * 16 + ((lane & 16) ? 8 : 0) + ((lane & 8) ? 4 : 0) + ((lane & 4) ? 2 : 0) +
+                          ((lane & 2) ? 1 : 0);
+          if (!(lane & 1) && m0 + row < p.M && top != 0ull) atomicMax(p.best + m0 + row, top);
+        }
+      }
     }
     if (p.split_k > 1) {
       if (do_store && threadIdx.x == 64) p.locks[tile] = 0;

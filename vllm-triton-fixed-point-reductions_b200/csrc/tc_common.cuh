@@ -1,6 +1,7 @@
 // tcgen05 / TMEM / TMA / mbarrier PTX wrappers and descriptor builders shared by the
 // tensor-core GEMM kernels (sm_100a only).
 #pragma once
+#include <cstring>
 
 #include <cuda.h>
 #include <stdint.h>
@@ -150,7 +151,22 @@ struct TcParams {
   int k_tile, split_k, int_bits; float scale, inv_scale;
   int tiles_m, tiles_n; uint32_t idesc; int b_kmajor; int c_vec_ok;
   int silu_mul;          // decode-shape kernel only: c[m, n / 2] = silu(out[m, n]) * out[m, n + 1], n even
+  // decode-shape kernel only: best[m] = max over columns of argmax_key(out[m, n], n_offset + n)
+  unsigned long long* best; unsigned int n_offset;
 };
+
+// (value, column) packed so that an unsigned 64-bit maximum picks the largest value and, among
+// equal values, the smallest column: the float's bits made order-preserving in the high word,
+// the inverted column in the low word.
+__host__ __device__ inline unsigned long long argmax_key(float v, unsigned int column) {
+#ifdef __CUDA_ARCH__
+  const unsigned int b = __float_as_uint(v);
+#else
+  unsigned int b; memcpy(&b, &v, 4);
+#endif
+  const unsigned int ord = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+  return ((unsigned long long)ord << 32) | (unsigned long long)(0xFFFFFFFFu - column);
+}
 
 template <int BN, int STAGES>
 struct SmemLayout {

@@ -520,6 +520,60 @@ def gemm_silu_mul(a, b_pairs, int_bits, fxp_frac_bits):
     return silu_mul_pairs(gemm_fxp_run(a, b_pairs, None, int_bits, fxp_frac_bits))
 
 
+def gemm_fxp_argmax(a, b, bias, int_bits, fxp_frac_bits, n_offset: int = 0):
+    """``gemm_fxp`` for at most 64 rows that also returns, per row, the arg-max key of the
+    outputs (``int64 [M]``, see ``argmax_from_keys``): greedy sampling straight from the lm_head
+    GEMM, with no pass over the ``[M, vocab]`` logits.  Keys of vocab shards (``n_offset`` = first
+    column of the shard) combine with ``combine_argmax_keys``.  Shapes the fused kernel does not
+    take fall back to ``gemm_fxp`` + a key built from ``torch.max``: same result."""
+    M, K = a.shape
+    N = b.shape[1]
+    c = torch.empty((M, N), device=a.device, dtype=a.dtype)
+    keys = torch.zeros((M,), device=a.device, dtype=torch.int64)
+    if M == 0 or N == 0:
+        return c, keys
+    cfg = get_runtime_config()
+    k_tile = _ovr.gemm_k_tile if _ovr.gemm_k_tile is not None else cfg.gemm_k_tile
+    if not k_tile:
+        k_tile = BLOCK_K_BY_DTYPE[a.dtype]
+    flags = (nat.GEMM_FORCE_PORTABLE if _ovr.gemm_portable else 0) | int(_ovr.gemm_flags)
+    st = nat.FXPR_ERR_UNSUPPORTED
+    if M <= 64 and a.dtype in (torch.float16, torch.bfloat16) and b.dtype == a.dtype:
+        if bias is not None and bias.dtype != a.dtype:
+            bias = bias.to(a.dtype)
+        with _on_device(a):
+            st = nat.load().fxpr_gemm_argmax(
+                a.data_ptr(), b.data_ptr(), nat.ptr(bias), c.data_ptr(), keys.data_ptr(), int(n_offset),
+                nat.DTYPE_CODE[a.dtype], M, N, K, a.stride(0), a.stride(1), b.stride(0), b.stride(1),
+                c.stride(0), int_bits, fxp_frac_bits, k_tile, flags, _status_word(a.device).data_ptr(),
+                nat.stream_ptr(a.device))
+    if st == nat.FXPR_ERR_UNSUPPORTED:
+        c = gemm_fxp_run(a, b, bias, int_bits, fxp_frac_bits)
+        return c, argmax_keys_of(c, n_offset)
+    nat.check(st, "gemm_fxp_argmax")
+    return c, keys
+
+
+def argmax_keys_of(logits, n_offset: int = 0):
+    """The key ``fxpr_gemm_argmax`` leaves for each row of ``logits`` (16-bit io dtypes)."""
+    v, idx = logits.max(dim=-1)                     # first maximal column, as torch.argmax
+    bits = v.float().view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+    ordv = torch.where(bits >= 0x80000000, (~bits) & 0xFFFFFFFF, bits | 0x80000000)
+    return ((ordv << 32) | (0xFFFFFFFF - (idx.to(torch.int64) + int(n_offset)))) ^ torch.iinfo(torch.int64).min ^ torch.iinfo(torch.int64).min
+
+
+def combine_argmax_keys(keys_list):
+    """Keys of several vocab shards -> keys of the whole row (unsigned 64-bit maximum)."""
+    flip = torch.iinfo(torch.int64).min
+    stacked = torch.stack([k ^ flip for k in keys_list], dim=0)     # signed order == unsigned order
+    return stacked.max(dim=0).values ^ flip
+
+
+def argmax_from_keys(keys):
+    """Winning column per row: the largest output, the smallest column among equals."""
+    return 0xFFFFFFFF - (keys & 0xFFFFFFFF)
+
+
 def gemm_fxp_int_into(a, b, out, int_bits, fxp_frac_bits):
     """``gemm_fxp_int`` into a caller-owned accumulator tensor (for example a peer-mapped
     buffer that other ranks read)."""

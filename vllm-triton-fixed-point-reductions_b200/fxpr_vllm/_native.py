@@ -83,6 +83,8 @@ SIGNATURES = {
     "fxpr_gemm": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i64, _i64, _i64,
                        _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i,
                        _vp, _i64, _vp, _vp, _vp]),
+    "fxpr_gemm_argmax": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64,
+                              _i, _i, _i, _i, _vp, _vp]),
     "fxpr_gemm_epilogue_from_int": (_i, [_vp, _i, _vp, _vp, _i, _i64, _i64, _i64, _i, _vp]),
     "fxpr_attention_scratch_bytes": (_i64, [_i64, _i, _i, _i, _i]),
     "fxpr_attention": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,

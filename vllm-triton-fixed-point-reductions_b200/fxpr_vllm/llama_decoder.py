@@ -26,8 +26,8 @@ import torch
 import torch.distributed as dist
 
 from . import library_ops as ops
-from ._lib import (BLOCK_K_BY_DTYPE, gemm_fxp_int_into, gemm_silu_mul, interleave_gate_up, rope_kv_write,
-                   silu_mul_pairs)
+from ._lib import (BLOCK_K_BY_DTYPE, argmax_from_keys, combine_argmax_keys, gemm_fxp_argmax, gemm_fxp_int_into,
+                   gemm_silu_mul, interleave_gate_up, rope_kv_write, silu_mul_pairs)
 from .config import get_runtime_config
 from .tp import check_shardable
 
@@ -66,6 +66,9 @@ class LocalGroup:
     def all_gather_cols(self, parts):
         return torch.cat(parts, dim=-1)
 
+    def all_gather_keys(self, parts):
+        return list(parts)
+
 
 class DistGroup:
     """One shard per process; ``torch.distributed`` carries the integer sums."""
@@ -91,6 +94,14 @@ class DistGroup:
         out = [torch.empty_like(parts[0]) for _ in range(self.size)]
         dist.all_gather(out, parts[0].contiguous(), group=self.group)
         return torch.cat(out, dim=-1)
+
+    def all_gather_keys(self, parts):
+        """Arg-max keys of this rank's vocab shard -> every shard's keys (8 bytes per row)."""
+        if self.size == 1 or self.skip_collectives:
+            return list(parts) * (self.size if self.skip_collectives else 1)
+        out = [torch.empty_like(parts[0]) for _ in range(self.size)]
+        dist.all_gather(out, parts[0].contiguous(), group=self.group)
+        return out
 
 
 def _full_weight(shape, seed, device, dtype, std):
@@ -119,6 +130,9 @@ class LlamaDecoder:
         # SiLU*mul inside the gate/up GEMM's epilogue for decode-sized batches (same bits as the
         # separate kernel); FXPR_DECODER_SILU_KERNEL=1 keeps the separate kernel (A/B timing)
         self.silu_epilogue = os.environ.get("FXPR_DECODER_SILU_KERNEL") != "1"
+        # captured greedy decode steps take the next token from the lm_head GEMM's arg-max keys
+        # instead of an argmax over the gathered logits; FXPR_DECODER_ARGMAX_KERNEL=1 keeps the latter
+        self.greedy_fused = fused_elementwise and os.environ.get("FXPR_DECODER_ARGMAX_KERNEL") != "1"
         tp = group.size
         if cfg.q_heads % tp or cfg.kv_heads % tp or cfg.ffn % tp or cfg.vocab % tp:
             raise ValueError(f"tp={tp} does not divide the head / ffn / vocab sizes")
@@ -218,9 +232,12 @@ class LlamaDecoder:
         return ops.rms_norm_fxp_from_int(accs[0], residual, norm_w, None, c.eps, c.frac_bits)
 
     # ------------------------------------------------------------------ forward
-    def forward(self, tokens, seq_ids, pos, qsl, seq_lens, max_q: int) -> torch.Tensor:
+    def forward(self, tokens, seq_ids, pos, qsl, seq_lens, max_q: int, greedy_keys: bool = False):
         """tokens/seq_ids/pos: [T] (flattened batch); returns the logits of each sequence's
-        last token, [B, vocab] in the io dtype, identical on every rank."""
+        last token, [B, vocab] in the io dtype, identical on every rank.  With ``greedy_keys``
+        the lm_head GEMM also leaves each row's arg-max key (no pass over the logits, and with
+        more than one rank only 8 bytes per row are exchanged): returns
+        ``(this rank's [B, vocab / tp] logits shards, next tokens [B])``."""
         c = self.cfg
         T, hd = tokens.numel(), c.head_dim
         shards = [self.shards[r] for r in self.group.local_ranks]
@@ -263,6 +280,12 @@ class LlamaDecoder:
             h = self._row_parallel_norm(acts, [sh.down[layer] for sh in shards], residual,
                                         self.norm_w[2 * layer + 2])
         last = h[(qsl[1:] - 1).long()]
+        if greedy_keys:
+            vs = c.vocab // self.group.size
+            both = [gemm_fxp_argmax(last, self.shards[r].lm_head, None, c.int_bits, c.frac_bits, n_offset=r * vs)
+                    for r in self.group.local_ranks]
+            keys = combine_argmax_keys(self.group.all_gather_keys([k for _, k in both]))
+            return [lg for lg, _ in both], argmax_from_keys(keys)
         parts = [ops.gemm_fxp(last, sh.lm_head, None, c.int_bits, c.frac_bits) for sh in shards]
         return self.group.all_gather_cols(parts)
 
@@ -304,8 +327,11 @@ class LlamaDecoder:
         self._g_qsl = torch.arange(B + 1, device=dev, dtype=torch.int32)
 
         def step():
+            if self.greedy_fused:
+                return self.forward(self._g_tok, self._g_ids, self._g_pos, self._g_qsl, self._g_lens, 1,
+                                    greedy_keys=True)
             logits = self.forward(self._g_tok, self._g_ids, self._g_pos, self._g_qsl, self._g_lens, 1)
-            return logits
+            return logits, self.greedy(logits)
 
         # eager warm-up on a side stream (allocations, split-K scratch, module state); it
         # writes the KV slot at start_len, which the first replay overwrites with the same data
@@ -317,12 +343,21 @@ class LlamaDecoder:
         torch.cuda.synchronize(dev)
         self._graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self._graph):
-            self._g_logits = step()
-            self._g_tok.copy_(self.greedy(self._g_logits))
+            self._g_logits, tok = step()
+            self._g_tok.copy_(tok)
             self._g_pos += 1
             self._g_lens += 1
 
-    def replay_decode(self) -> torch.Tensor:
-        """One captured decode step; returns the logits buffer (overwritten by the next replay)."""
+    def replay_decode(self):
+        """One captured decode step; returns the logits buffer (overwritten by the next replay):
+        the full ``[B, vocab]`` tensor, or with ``greedy_fused`` this rank's vocab shards (see
+        ``last_logits``)."""
         self._graph.replay()
+        return self._g_logits
+
+    def last_logits(self) -> torch.Tensor:
+        """The ``[B, vocab]`` logits of the last replayed step on every rank (with ``greedy_fused``
+        the shards are gathered here, outside the step)."""
+        if self.greedy_fused:
+            return self.group.all_gather_cols(list(self._g_logits))
         return self._g_logits
