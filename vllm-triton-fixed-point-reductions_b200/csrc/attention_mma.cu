@@ -129,7 +129,7 @@ static int launch_mma(const AttnParams& p, const MmaAttnShape& sh, cudaStream_t 
 template <typename T, int HD, int NW, bool ACC64, bool ROWS8, int NSTAGE = 2, int MINB = 4>
 static int launch_decode(const AttnParams& p, const MmaAttnShape& sh, cudaStream_t s) {
   constexpr int kTileBytes = kTileN * HD * 2;
-  const size_t smem = (size_t)16 * HD * 2 + NSTAGE * (size_t)kTileBytes + NW * 16 * 4 + NW * 16 * 8 +
+  const size_t smem = (size_t)(ROWS8 ? 8 : 16) * HD * 2 + NSTAGE * (size_t)kTileBytes + NW * 16 * 4 + NW * 16 * 8 +
                       (size_t)sh.stash_keys * stash_bytes_per_key(sh.stash_rows);
   auto k = attn_decode_kernel<T, HD, NW, ACC64, ROWS8, NSTAGE, MINB>;
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);

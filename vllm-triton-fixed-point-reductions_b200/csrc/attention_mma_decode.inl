@@ -27,8 +27,9 @@ attn_decode_kernel(const AttnParams p, const MmaAttnShape sh) {
   using AccT = typename IntOf<ACC64 ? 64 : 32>::type;
 
   extern __shared__ __align__(128) uint8_t smem[];
-  uint8_t* q_s = smem;                                            // 16 x HD
-  uint8_t* stage_s = q_s + 16 * HD * 2;
+  constexpr int QR = ROWS8 ? 8 : 16;               // Q rows kept in shared memory (rows 8..15 of the MMA tile are zero registers)
+  uint8_t* q_s = smem;                                            // QR x HD
+  uint8_t* stage_s = q_s + QR * HD * 2;
   float* rmax_s = reinterpret_cast<float*>(stage_s + NSTAGE * kTileBytes);        // [NW][16]
   long long* den_s = reinterpret_cast<long long*>(rmax_s + NW * 16);              // [NW][16]
   float* stash_s = reinterpret_cast<float*>(den_s + NW * 16);
@@ -77,7 +78,7 @@ attn_decode_kernel(const AttnParams p, const MmaAttnShape sh) {
     r_slope[h] = (p.alibi && valid) ? p.alibi[kvh * G + r % G] : 0.0f;
   }
 
-  for (int idx = threadIdx.x; idx < 16 * RC; idx += NT) {
+  for (int idx = threadIdx.x; idx < QR * RC; idx += NT) {
     const int r = idx / RC, c = idx % RC;
     const int tok = tok0 + r / G;
     const bool v = tok < q_len;
@@ -171,8 +172,14 @@ attn_decode_kernel(const AttnParams p, const MmaAttnShape sh) {
 #pragma unroll
       for (int kk2 = 0; kk2 < HD / 32; ++kk2) {
         uint32_t a0[4], a1[4];
-        ldsm_x4(qs_addr + swz<RC>(lane & 15, kk2 * 4 + (lane >> 4)), a0[0], a0[1], a0[2], a0[3]);
-        ldsm_x4(qs_addr + swz<RC>(lane & 15, kk2 * 4 + 2 + (lane >> 4)), a1[0], a1[1], a1[2], a1[3]);
+        if (ROWS8) {
+          // eight live rows: one load brings rows 0..7 of four 8-wide k chunks
+          ldsm_x4(qs_addr + swz<RC>(lane & 7, kk2 * 4 + (lane >> 3)), a0[0], a0[2], a1[0], a1[2]);
+          a0[1] = a0[3] = a1[1] = a1[3] = 0u;
+        } else {
+          ldsm_x4(qs_addr + swz<RC>(lane & 15, kk2 * 4 + (lane >> 4)), a0[0], a0[1], a0[2], a0[3]);
+          ldsm_x4(qs_addr + swz<RC>(lane & 15, kk2 * 4 + 2 + (lane >> 4)), a1[0], a1[1], a1[2], a1[3]);
+        }
 #pragma unroll
         for (int jj = 0; jj < JW; ++jj) {
           const int j = warp * JW + jj;

@@ -660,7 +660,8 @@ def pick_num_splits_b200(requested, num_requests, max_query_len, num_heads, num_
         # with 8.
         tiles = -(-max_keys // 64)
         key_bytes = 4 * g if g <= 8 else 64
-        cap_tiles = max(1, (19968 // key_bytes) // 64)
+        budget = 19968 + (2048 if g <= 8 else 0)      # eight-row Q tiles leave 2 KB more
+        cap_tiles = max(1, (budget // key_bytes) // 64)
         by_keys = -(-tiles // cap_tiles)
         by_keys = 8 if by_keys > 4 else max(1, by_keys)
         clusters = max(1, num_requests * num_kv_heads)
