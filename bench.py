@@ -418,6 +418,27 @@ def bench_llama(dev, dist, world, peaks, batch=64, prompt_len=1024, gen=256):
     logits, prefill_ms = timed(lambda: model.prefill(prompts))
     d_prefill = _digest(logits)
     state = {"tok": model.greedy(logits), "logits": logits}
+    peer_note = None
+    if model.peer is not None:
+        # one eager decode step through each exchange before anything is timed: the peer-memory
+        # kernel must reproduce the ncclAllReduce path bit for bit on every rank and report no
+        # timed-out wait, else the run continues on ncclAllReduce (the default exchange)
+        from fxpr_vllm import _lib as L
+
+        peer, model.peer = model.peer, None
+        want = model.decode_step(state["tok"], prompt_len)
+        model.peer = peer
+        got = model.decode_step(state["tok"], prompt_len)
+        ok = bool(torch.equal(want, got))
+        try:
+            L.check_device_status(dev)
+        except RuntimeError:
+            ok = False
+        flag = torch.tensor([1 if ok else 0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) != 1:
+            model.peer = None
+            peer_note = "peer-memory exchange failed its self-check on this box; ncclAllReduce used"
 
     def decode_all():
         for step in range(gen):
@@ -458,6 +479,9 @@ def bench_llama(dev, dist, world, peaks, batch=64, prompt_len=1024, gen=256):
         "last_tokens_digest": int((state["tok"] * (torch.arange(batch, device=dev) + 1)).sum().item()),
         "build_s": build_s,
         "launch": launch, "graph_error": graph_error, "tp_scaling": tp_scaling,
+        "exchange": ("single GPU" if dist is None else
+                     "peer-memory reduce+norm kernel" if model.peer is not None else "ncclAllReduce + norm kernel"),
+        "exchange_note": peer_note,
         "note": "digests are equal across TP degrees when the integer all-reduce keeps the logits "
                 "bit-identical",
     }

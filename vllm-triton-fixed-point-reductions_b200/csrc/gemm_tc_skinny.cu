@@ -197,32 +197,50 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_co
       const int rows_per = (MP + S - 1) / S, mr0 = rank * rows_per;   // any S <= 8; the last rank may get fewer
       const int tile = (int)blockIdx.y;
       const T* bias = (const T*)p.bias;
-      for (int idx = (int)threadIdx.x - 64; idx < rows_per * 128; idx += EPIW * 32) {
-        const int m = mr0 + idx / 128, nl = idx % 128, n = tile * 128 + nl;
-        const bool live = m < MP && m < p.M && n < p.N;
-        long long q = 0;
-        if (live)
-          for (int rr = 0; rr < S; ++rr) q += cluster.map_shared_rank(red, rr)[m * 128 + nl];
-        if (p.int_bits != 64) q = (long long)(int32_t)q;
+      // Two neighbouring columns per thread and step: one 16-byte read per rank.  (Reads over
+      // distributed shared memory are paced per request, ~100 clocks per warp request whatever
+      // its width -- issuing more of them at once made the merge slower -- so wider requests are
+      // what shortens it.)
+      const long long* peer[8];
+      for (int rr = 0; rr < S; ++rr) peer[rr] = cluster.map_shared_rank(red, rr);
+      for (int idx = (int)threadIdx.x - 64; idx < rows_per * 64; idx += EPIW * 32) {
+        const int m = mr0 + idx / 64, nl = (idx % 64) * 2, n = tile * 128 + nl;
+        if (m >= MP || m >= p.M || n >= p.N) continue;
+        long long q0 = 0, q1 = 0;
+        for (int rr = 0; rr < S; ++rr) {
+          const longlong2 v = *reinterpret_cast<const longlong2*>(peer[rr] + m * 128 + nl);
+          q0 += v.x;
+          q1 += v.y;
+        }
+        if (p.int_bits != 64) { q0 = (long long)(int32_t)q0; q1 = (long long)(int32_t)q1; }
+        const bool two = n + 1 < p.N;
         if (p.silu_mul) {
-          // (gate, up) column pairs sit in neighbouring lanes (idx runs with the lane)
-          float v = fixed_to_float<long long>(q, p.inv_scale);
-          if (bias && live) v = __fadd_rn(v, to_f32<T>(bias[n]));
-          const float mine = to_f32<T>(from_f32<T>(v));
-          const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
-          if (live && !(nl & 1) && n + 1 < p.N)
-            ((T*)p.c)[(int64_t)m * p.c_sm + (n >> 1)] = silu_mul_io<T>(mine, other);
+          // the (gate, up) pair of output column n / 2
+          if (!two) continue;
+          float g = fixed_to_float<long long>(q0, p.inv_scale), u = fixed_to_float<long long>(q1, p.inv_scale);
+          if (bias) { g = __fadd_rn(g, to_f32<T>(bias[n])); u = __fadd_rn(u, to_f32<T>(bias[n + 1])); }
+          ((T*)p.c)[(int64_t)m * p.c_sm + (n >> 1)] =
+              silu_mul_io<T>(to_f32<T>(from_f32<T>(g)), to_f32<T>(from_f32<T>(u)));
           continue;
         }
-        if (!live) continue;
         if (p.c_int) {
-          if (p.int_bits == 64) ((long long*)p.c_int)[(int64_t)m * p.N + n] = q;
-          else ((int32_t*)p.c_int)[(int64_t)m * p.N + n] = (int32_t)q;
+          if (p.int_bits == 64) {
+            ((long long*)p.c_int)[(int64_t)m * p.N + n] = q0;
+            if (two) ((long long*)p.c_int)[(int64_t)m * p.N + n + 1] = q1;
+          } else {
+            ((int32_t*)p.c_int)[(int64_t)m * p.N + n] = (int32_t)q0;
+            if (two) ((int32_t*)p.c_int)[(int64_t)m * p.N + n + 1] = (int32_t)q1;
+          }
         }
         if (p.c) {
-          float v = fixed_to_float<long long>(q, p.inv_scale);
-          if (bias) v = __fadd_rn(v, to_f32<T>(bias[n]));
-          ((T*)p.c)[(int64_t)m * p.c_sm + n] = from_f32<T>(v);
+          float v0 = fixed_to_float<long long>(q0, p.inv_scale), v1 = fixed_to_float<long long>(q1, p.inv_scale);
+          if (bias) {
+            v0 = __fadd_rn(v0, to_f32<T>(bias[n]));
+            if (two) v1 = __fadd_rn(v1, to_f32<T>(bias[n + 1]));
+          }
+          T* dst = (T*)p.c + (int64_t)m * p.c_sm + n;
+          dst[0] = from_f32<T>(v0);
+          if (two) dst[1] = from_f32<T>(v1);
         }
       }
     }
