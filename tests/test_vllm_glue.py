@@ -161,6 +161,7 @@ def test_quant_config_surface():
     layer = torch.nn.Module()
     m.create_weights(layer, 8, [5, 3], 8, 8, torch.float32)
     assert layer.weight.shape == (8, 8)
+    layer.weight.data.copy_(torch.arange(64.0).reshape(8, 8))   # create_weights leaves it uninitialised (may hold NaN)
     idx = torch.tensor([1, 7])
     assert torch.equal(m.embedding(layer, idx), layer.weight[idx])
 

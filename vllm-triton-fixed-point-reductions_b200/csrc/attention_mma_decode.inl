@@ -325,6 +325,16 @@ attn_decode_kernel(const AttnParams p, const MmaAttnShape sh) {
       wv_s[(size_t)r * HD + d + 1] = (long long)acc[jj][2 * h + 1];
     }
   }
+  // One denominator per row and CTA (not one per warp): reads over distributed shared memory are
+  // paced per request, so the merge below asks for as few and as wide ones as it can.
+  __syncthreads();
+  long long den_row = 0;
+  if (threadIdx.x < 16) {
+#pragma unroll
+    for (int w = 0; w < NW; ++w) den_row += den_s[w * 16 + threadIdx.x];
+  }
+  __syncthreads();
+  if (threadIdx.x < 16) den_s[threadIdx.x] = den_row;
   cluster.sync();
   {
     // Every rank merges its own slice of the head dimension (integer sums over the ranks are
@@ -333,20 +343,28 @@ attn_decode_kernel(const AttnParams p, const MmaAttnShape sh) {
     const int cpr = (HD + S - 1) / S;                // columns per rank
     const int c0 = rank * cpr;
     const int ncol = max(0, min(HD, c0 + cpr) - c0);
-    for (int idx = threadIdx.x; idx < rows_here * ncol; idx += NT) {
-      const int r = idx / ncol, d = c0 + idx % ncol;
-      long long dsum = 0, wsum = 0;
+    const bool pairs = ((cpr | ncol) & 1) == 0;      // then c0 is even too: 16-byte reads
+    const int per_row = pairs ? ncol / 2 : ncol;
+    for (int idx = threadIdx.x; idx < rows_here * per_row; idx += NT) {
+      const int r = idx / per_row, d = c0 + (pairs ? 2 : 1) * (idx % per_row);
+      long long dsum = 0, w0 = 0, w1 = 0;
       for (int rr = 0; rr < S; ++rr) {
-        const long long* dp = cluster.map_shared_rank(den_s, rr);
-#pragma unroll
-        for (int w = 0; w < NW; ++w) dsum += dp[w * 16 + r];
-        wsum += cluster.map_shared_rank(wv_s, rr)[(size_t)r * HD + d];
+        dsum += cluster.map_shared_rank(den_s, rr)[r];
+        const long long* wp = cluster.map_shared_rank(wv_s, rr) + (size_t)r * HD + d;
+        if (pairs) {
+          const longlong2 v = *reinterpret_cast<const longlong2*>(wp);
+          w0 += v.x;
+          w1 += v.y;
+        } else {
+          w0 += wp[0];
+        }
       }
       const float dn = fmaxf(fixed_to_float<long long>(wrap_to_bits(dsum, p.int_bits), p.inv_scale), 1.0e-6f);
-      const float num = fixed_to_float<long long>(wrap_to_bits(wsum, p.int_bits), p.inv_scale);
       const int tok = tok0 + r / G, head = kvh * G + r % G;
       T* op = (T*)p.o + (int64_t)(q_start + tok) * p.o_st + (int64_t)head * p.o_sh;
-      op[d] = from_f32<T>(__fdiv_rn(num, dn));
+      op[d] = from_f32<T>(__fdiv_rn(fixed_to_float<long long>(wrap_to_bits(w0, p.int_bits), p.inv_scale), dn));
+      if (pairs)
+        op[d + 1] = from_f32<T>(__fdiv_rn(fixed_to_float<long long>(wrap_to_bits(w1, p.int_bits), p.inv_scale), dn));
     }
   }
   cluster.sync();
