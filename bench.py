@@ -420,10 +420,15 @@ def bench_llama(dev, dist, world, peaks, batch=64, prompt_len=1024, gen=256):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return out, float(ms.item())
 
+    peer_setup_error = None
     if dist is not None and os.environ.get("FXPR_BENCH_NCCL_EXCHANGE") != "1":
         # decode-sized batches exchange through the peer-memory reduce + norm kernel (same bits);
         # the prefill below is too large for its buffers and takes the ncclAllReduce path
-        model.enable_peer_reduce()
+        try:
+            model.enable_peer_reduce()
+        except RuntimeError as e:            # raised on every rank or on none: the run goes on with ncclAllReduce
+            model.peer = None
+            peer_setup_error = repr(e)[:200]
     logits, prefill_ms = timed(lambda: model.prefill(prompts))
     d_prefill = _digest(logits)
     state = {"tok": model.greedy(logits), "logits": logits}
@@ -490,7 +495,7 @@ def bench_llama(dev, dist, world, peaks, batch=64, prompt_len=1024, gen=256):
         "launch": launch, "graph_error": graph_error, "tp_scaling": tp_scaling,
         "exchange": ("single GPU" if dist is None else
                      "peer-memory reduce+norm kernel" if model.peer is not None else "ncclAllReduce + norm kernel"),
-        "exchange_note": peer_note,
+        "exchange_note": peer_note or peer_setup_error,
         "note": "digests are equal across TP degrees when the integer all-reduce keeps the logits "
                 "bit-identical",
     }

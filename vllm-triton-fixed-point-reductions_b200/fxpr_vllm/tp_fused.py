@@ -67,23 +67,45 @@ class PeerReduceNorm:
                                                 *[ctypes.byref(o) for o in off]), "tp_buffer_bytes")
         self.acc_off, self.res_off, self.y_off, self.flags_off, self.nbytes = (o.value for o in off)
         self._owned, self._opened = [], []
+        # Set-up is collective.  A rank whose allocation or mapping fails still takes part in
+        # every exchange below, and the outcome is agreed on at the end, so that either every
+        # rank gets the object or every rank raises (no rank is left waiting in a collective).
+        failure = None
+        own, handle = 0, b""
+        bases = [None] * self.world
         with _on_device(torch.empty(0, device=self.device)):
-            own, handle = self._alloc()
-            bases = [None] * self.world
-            bases[self.rank] = own
-            if _fake_world:
-                for p in range(1, _fake_world):
-                    bases[p], _ = self._alloc()
-            elif self.world > 1:
+            try:
+                own, handle = self._alloc()
+                bases[self.rank] = own
+                if _fake_world:
+                    for p in range(1, _fake_world):
+                        bases[p], _ = self._alloc()
+            except (RuntimeError, ValueError, TypeError) as e:
+                failure = f"allocation: {e}"
+            if self.world > 1 and not _fake_world:
                 handles = [None] * self.world
-                dist.all_gather_object(handles, handle, group=group)
-                for p in range(self.world):
-                    if p != self.rank:
-                        ptr = ctypes.c_void_p()
-                        buf = (ctypes.c_char * 64).from_buffer_copy(handles[p])
-                        nat.check(self.lib.fxpr_tp_open(buf, ctypes.byref(ptr)), "tp_open")
-                        self._opened.append(ptr.value)
-                        bases[p] = ptr.value
+                dist.all_gather_object(handles, handle if failure is None else None, group=group)
+                if failure is None and any(h is None for h in handles):
+                    failure = "a peer could not allocate its buffer"
+                if failure is None:
+                    try:
+                        for p in range(self.world):
+                            if p != self.rank:
+                                ptr = ctypes.c_void_p()
+                                buf = (ctypes.c_char * 64).from_buffer_copy(handles[p])
+                                nat.check(self.lib.fxpr_tp_open(buf, ctypes.byref(ptr)), "tp_open")
+                                self._opened.append(ptr.value)
+                                bases[p] = ptr.value
+                    except (RuntimeError, ValueError, TypeError) as e:
+                        failure = f"mapping a peer's buffer: {e}"
+                ok = torch.tensor([0 if failure else 1], device=self.device)
+                dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)    # also: every buffer is zeroed and mapped
+                if int(ok.item()) != 1 and failure is None:
+                    failure = "a peer could not map the buffers"
+        if failure is not None:
+            self.acc = self.residual = self.y = None
+            self._release()
+            raise RuntimeError(f"PeerReduceNorm set-up failed on rank {self.rank}: {failure}")
         self._bases = (ctypes.c_void_p * self.world)(*bases)
         self.ctl = torch.zeros(2, dtype=torch.int32, device=self.device)
         isz, osz = int_bits // 8, torch.empty(0, dtype=io_dtype).element_size()
@@ -93,8 +115,6 @@ class PeerReduceNorm:
             .view(io_dtype).view(max_rows, hidden)
         self.y = _window(own + self.y_off, max_rows * hidden * osz, self.device) \
             .view(io_dtype).view(max_rows, hidden)
-        if self.world > 1 and not _fake_world:
-            dist.barrier(group=group)          # every rank's buffer is zeroed and mapped
 
     def _alloc(self):
         ptr = ctypes.c_void_p()
@@ -127,13 +147,15 @@ class PeerReduceNorm:
         torch.cuda.synchronize(self.device)
         if self.world > 1 and self._opened and dist.is_initialized():
             dist.barrier(group=self.group)
-        had_peers = bool(self._opened)
+        self.acc = self.residual = self.y = None
+        self._release(barrier=bool(self._opened) and dist.is_initialized())
+
+    def _release(self, barrier: bool = False) -> None:
         for p in self._opened:
             self.lib.fxpr_tp_close(ctypes.c_void_p(p))
         self._opened = []
-        if had_peers and dist.is_initialized():
+        if barrier:
             dist.barrier(group=self.group)     # nobody still maps the buffer freed below
-        self.acc = self.residual = self.y = None
         for p in self._owned:
             self.lib.fxpr_tp_free(ctypes.c_void_p(p))
         self._owned = []
