@@ -50,11 +50,12 @@
           screen |= v[i] | v[i + 1];
         }
       };
-      tmem_ld16(ta0, va); tmem_wait_ld_regs(va); convert(va, 0, screen0);
-      tmem_ld16(ta0 + 16, vb); tmem_wait_ld_regs(vb); convert(vb, 1, screen0);
+      // both halves of a buffer are requested before the one wait
+      tmem_ld16(ta0, va); tmem_ld16(ta0 + 16, vb); tmem_wait_ld_regs2(va, vb);
+      convert(va, 0, screen0); convert(vb, 1, screen0);
       if (nbuf == 2) {
-        tmem_ld16(ta1, va); tmem_wait_ld_regs(va); convert(va, 0, screen1);
-        tmem_ld16(ta1 + 16, vb); tmem_wait_ld_regs(vb); convert(vb, 1, screen1);
+        tmem_ld16(ta1, va); tmem_ld16(ta1 + 16, vb); tmem_wait_ld_regs2(va, vb);
+        convert(va, 0, screen1); convert(vb, 1, screen1);
       }
       if (__any_sync(0xffffffffu, ((screen0 | screen1) & 0x40000000u) != 0)) {
         if (!corr_used) {
