@@ -32,6 +32,7 @@
 //               tensor core works on the next tile.
 // KV splits are not handled here (the dispatcher sends them to attention_mma.cu: same bits).
 // Every wait is bounded; on a time-out the CTA sets the status word and leaves.
+#include <algorithm>
 #include <cuda.h>
 
 #include "attention_common.cuh"
@@ -131,11 +132,12 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t q_s = smem_base, stage0 = smem_base + kQBytes, p_s0 = stage0 + kTcStages * kStageBytes;
   const uint32_t bar_base = smem_base + kBarOffset;
-  // barriers: qfull | full[4] empty[4] | sfull[2] sfree[2] | pready[2] | pvfull[2] pvfree[2] | sync
+  // barriers: qfull | full[4] empty[4] | sfull[2] sfree[2] | pready[2] | pvfull[2] pvfree[2] | sync | qfree
   const uint32_t qfull = bar_base, full0 = bar_base + 8, empty0 = full0 + 8 * kTcStages;
   const uint32_t sfull0 = empty0 + 8 * kTcStages, sfree0 = sfull0 + 16, pready0 = sfree0 + 16;
   const uint32_t pvfull0 = pready0 + 16, pvfree0 = pvfull0 + 16, soft_bar = pvfree0 + 16;
-  constexpr int kMisc = 8 * (1 + 2 * kTcStages + 10 + 1);
+  const uint32_t qfree = soft_bar + 8;
+  constexpr int kMisc = 8 * (1 + 2 * kTcStages + 10 + 2);
   volatile uint32_t* tmem_slot = (volatile uint32_t*)(smem_gen + kBarOffset + kMisc);
   volatile int* abort_flag = (volatile int*)(smem_gen + kBarOffset + kMisc + 8);
   float* rmax_s = (float*)(smem_gen + kBarOffset + kMisc + 16);                 // [CG][128]
@@ -143,22 +145,36 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  // ---- which rows and keys ----------------------------------------------------------
+  // ---- work items ---------------------------------------------------------------------
+  // Persistent CTAs: CTA b takes the work items b, b + gridDim.x, ... of the padded space
+  // (request, row block, KV head), later row blocks (more keys) first.  Every role walks the
+  // same list and keeps its ring positions and barrier phases running from one item to the
+  // next, so the producer fetches the next item's Q and first keys and the MMA warp starts its
+  // scores while the softmax warps still convert and store the current item's output.
   const int hkv = p.num_kv_heads;
-  const int qb = blockIdx.x / hkv, kvh = blockIdx.x % hkv;
-  const int req = blockIdx.y;
-  const int q_start = p.qsl[req], q_len = p.qsl[req + 1] - q_start;
   const int G = sh.rows_per_token;
-  const int tok0 = qb * sh.tokens_per_block;
-  if (tok0 >= q_len) return;                               // uniform over the CTA, before any barrier
-  const int seq_len = p.seq_lens[req];
-  const int ctx = seq_len - q_len;
-  const int tok_end = min(q_len, tok0 + sh.tokens_per_block);
-  const int hi_key = p.causal ? min(seq_len, ctx + tok_end) : seq_len;
-  const int lo_key = p.window > 0 ? max(0, ctx + tok0 - p.window + 1) : 0;
-  const int t0 = lo_key / kTcTileN;
-  const int t1 = max(t0, (hi_key + kTcTileN - 1) / kTcTileN);
-  const int n_tiles = t1 - t0;
+  const int items_per_req = sh.num_q_blocks * hkv;
+  const int total_items = items_per_req * p.num_reqs;
+  struct Item { int live, req, kvh, q_start, q_len, tok0, seq_len, ctx, t0, t1; };
+  auto decode_item = [&](int w) -> Item {
+    Item I;
+    I.req = w / items_per_req;
+    const int rem = w - I.req * items_per_req;
+    const int qb = sh.num_q_blocks - 1 - rem / hkv;
+    I.kvh = rem % hkv;
+    I.q_start = p.qsl[I.req];
+    I.q_len = p.qsl[I.req + 1] - I.q_start;
+    I.tok0 = qb * sh.tokens_per_block;
+    I.live = I.tok0 < I.q_len;
+    I.seq_len = I.live ? p.seq_lens[I.req] : 0;
+    I.ctx = I.seq_len - I.q_len;
+    const int tok_end = min(I.q_len, I.tok0 + sh.tokens_per_block);
+    const int hi_key = p.causal ? min(I.seq_len, I.ctx + tok_end) : I.seq_len;
+    const int lo_key = p.window > 0 ? max(0, I.ctx + I.tok0 - p.window + 1) : 0;
+    I.t0 = lo_key / kTcTileN;
+    I.t1 = max(I.t0, (hi_key + kTcTileN - 1) / kTcTileN);
+    return I;
+  };
 
   if (threadIdx.x == 32) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
@@ -167,6 +183,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   }
   if (threadIdx.x == 0) {
     mbar_init(qfull, 1);
+    mbar_init(qfree, 1);
     for (int s = 0; s < kTcStages; ++s) { mbar_init(full0 + 8u * s, 1); mbar_init(empty0 + 8u * s, 1); }
     for (int b = 0; b < 2; ++b) {
       mbar_init(sfull0 + 8u * b, 1); mbar_init(sfree0 + 8u * b, kTcSoftWarps);
@@ -196,12 +213,29 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // lanes in one instruction: issued one by one they cost the issuing thread ~80 clocks
     // each.  Nothing is copied, and the block table is not read, past the end of the
     // sequence; V rows there are cleared by the MMA warp before P.V.
-    const int32_t* bt = p.block_table + (int64_t)req * p.bt_stride;
     int stage = 0; uint32_t phase = 1;
+    uint32_t q_phase = 1;                                    // qfree: the first wait passes
     // Block-table entries are read 32 at a time (lane L: the 16-key group L of an 8-tile
     // block), one block ahead of their use, and handed round by shuffle.
     int page_shift = -1;
     for (int b = 4; b < 31; ++b) if ((1 << b) == sh.page_size) page_shift = b;
+    for (int w = blockIdx.x; w < total_items; w += gridDim.x) {
+    const Item I = decode_item(w);
+    if (!I.live) continue;
+    const int kvh = I.kvh, seq_len = I.seq_len, t0 = I.t0, t1 = I.t1;
+    const int32_t* bt = p.block_table + (int64_t)I.req * p.bt_stride;
+    // Q rows: box {64 dims, G heads, 128 / G tokens} -> row = token * G + head.  Tokens past
+    // this request's (they belong to the next one, or lie beyond the tensor: zeros) are rows
+    // whose every key is masked and that are never stored.  The buffer is free once the MMA
+    // warp's last score MMA of the previous item has completed.
+    if (!__all_sync(0xffffffffu, mbar_wait(qfree, q_phase, abort_flag))) goto producer_done;
+    q_phase ^= 1;
+    if (lane == 0) {
+      mbar_expect_tx(qfull, kQBytes);
+      tma_load_3d(q_s, &map_q, qfull, 0, kvh * G, I.q_start + I.tok0);
+      tma_load_3d(q_s + kQBytes / 2, &map_q, qfull, 64, kvh * G, I.q_start + I.tok0);
+    }
+    __syncwarp();
     auto load_entries = [&](int tb) -> int {
       const int n = tb * kTcTileN + lane * 16;
       return (tb < t1 && n < seq_len) ? bt[page_shift >= 0 ? (n >> page_shift) : (n / sh.page_size)] : 0;
@@ -238,6 +272,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         cur = nxt;
       }
     }
+    }
   producer_done:;
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ----------------------------------------
@@ -257,20 +292,18 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
       __syncwarp();
     };
-    if (lane == 0) {
-      // Q rows: box {64 dims, G heads, 128 / G tokens} -> row = token * G + head.  Tokens past
-      // this request's (they belong to the next one, or lie beyond the tensor: zeros) are
-      // rows whose every key is masked and that are never stored.
-      mbar_expect_tx(qfull, kQBytes);
-      tma_load_3d(q_s, &map_q, qfull, 0, kvh * G, q_start + tok0);
-      tma_load_3d(q_s + kQBytes / 2, &map_q, qfull, 64, kvh * G, q_start + tok0);
-    }
-    __syncwarp();
-    bool okq = mbar_wait(qfull, 0, abort_flag);
+    int stage = 0; uint32_t phase = 0;
+    int it = 0;                                              // S tiles issued so far (all items, both passes)
+    int jg = 0;                                              // P.V tiles issued so far (all items)
+    uint32_t q_phase = 0;
+    for (int w = blockIdx.x; w < total_items; w += gridDim.x) {
+    const Item I = decode_item(w);
+    if (!I.live) continue;
+    const int seq_len = I.seq_len, t0 = I.t0, t1 = I.t1, n_tiles = I.t1 - I.t0;
+    bool okq = mbar_wait(qfull, q_phase, abort_flag);
     if (!__all_sync(0xffffffffu, okq)) goto issuer_done;
+    q_phase ^= 1;
     {
-      int stage = 0; uint32_t phase = 0;
-      int it = 0;                                            // S tiles issued so far (both passes)
       // pass A: scores only
       for (int t = t0; t < t1; ++t, ++it) {
         const int sb = it & 1; const uint32_t sph = ((it >> 1) & 1) ^ 1;
@@ -297,9 +330,15 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         return true;
       };
       if (n_tiles > 0 && !issue_s_next()) goto issuer_done;
-      for (int j = 0; j < n_tiles; ++j) {
-        if (j + 1 < n_tiles && !issue_s_next()) goto issuer_done;
-        const int b = j & 1; const uint32_t ph = (j >> 1) & 1;
+      if (n_tiles <= 1 && lane == 0) umma_commit(qfree);     // the item's last score MMA is issued
+      __syncwarp();
+      for (int j = 0; j < n_tiles; ++j, ++jg) {
+        if (j + 1 < n_tiles) {
+          if (!issue_s_next()) goto issuer_done;
+          if (j + 2 == n_tiles && lane == 0) umma_commit(qfree);
+          __syncwarp();
+        }
+        const int b = jg & 1; const uint32_t ph = (jg >> 1) & 1;
         const bool r1 = mbar_wait(pready0 + 8u * b, ph, abort_flag);
         const bool r2 = mbar_wait(pvfree0 + 8u * b, ph ^ 1, abort_flag);
         if (!__all_sync(0xffffffffu, r1 && r2)) goto issuer_done;
@@ -335,6 +374,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (++stage == kTcStages) { stage = 0; phase ^= 1; }
       }
     }
+    }
   issuer_done:;
   } else if (warp >= kTcFirstSoft) {
     // ------------------------------ softmax / conversion warps ------------------------
@@ -342,12 +382,6 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int half = (warp - kTcFirstSoft) >> 2;                        // which quarter of the columns
     const int row = quarter * 32 + lane;                     // tensor-memory lane = query row
     const uint32_t lane_sel = (uint32_t)(quarter * 32) << 16;
-    const int tok = tok0 + row / G, head = kvh * G + row % G;
-    const bool valid = tok < q_len;
-    const int pos = ctx + tok;
-    const int kend = valid ? (p.causal ? min(seq_len, pos + 1) : seq_len) : 0;
-    const int kbeg = valid ? (p.window > 0 ? max(0, pos - p.window + 1) : 0) : 0;
-    const float slope = (p.alibi && valid) ? p.alibi[head] : 0.0f;
     const float ninf = -__int_as_float(0x7f800000);
     const bool plain_scores = !(p.cap_log2 > 0.0f) && p.alibi == nullptr;
     const float magic = __uint_as_float(kMagicBits);
@@ -360,6 +394,19 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       soft_phase ^= 1;
       return done;
     };
+    int it = 0;                                              // S tiles consumed so far (all items, both passes)
+    int jg = 0;                                              // P.V tiles of the items before this one
+    for (int w = blockIdx.x; w < total_items && ok; w += gridDim.x) {
+    const Item I = decode_item(w);
+    if (!I.live) continue;
+    const int kvh = I.kvh, q_start = I.q_start, q_len = I.q_len, tok0 = I.tok0, seq_len = I.seq_len, ctx = I.ctx;
+    const int t0 = I.t0, t1 = I.t1, n_tiles = I.t1 - I.t0;
+    const int tok = tok0 + row / G, head = kvh * G + row % G;
+    const bool valid = tok < q_len;
+    const int pos = ctx + tok;
+    const int kend = valid ? (p.causal ? min(seq_len, pos + 1) : seq_len) : 0;
+    const int kbeg = valid ? (p.window > 0 ? max(0, pos - p.window + 1) : 0) : 0;
+    const float slope = (p.alibi && valid) ? p.alibi[head] : 0.0f;
     // scores of this thread's 32 keys of tile t, in log2 space, masked (attention.py:103-121, 249-254)
     auto load_scores = [&](int it, int t, float (&s)[KT]) -> bool {
       const int sb = it & 1; const uint32_t sph = (it >> 1) & 1;
@@ -390,7 +437,6 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
     // =============================== pass A: row maxima ===============================
     float rmax = ninf;
-    int it = 0;
     for (int t = t0; t < t1 && ok; ++t, ++it) {
       float s[KT];
       if (!load_scores(it, t, s)) { ok = false; break; }
@@ -418,7 +464,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     bool corr_used = false;
 
     // round the P.V partial of tile j (this thread's 64 columns) to Q-format and add it
-    auto convert_pv = [&](int j) -> bool {
+    auto convert_pv = [&](int j) -> bool {                  // j counts over all items
       const int b = j & 1; const uint32_t ph = (j >> 1) & 1;
       if (!warp_wait_relaxed(pvfull0 + 8u * b, ph, abort_flag, lane)) return false;
       tc_fence_after();
@@ -459,7 +505,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       if (!load_scores(it, t, s)) { ok = false; break; }
       // weights, integer denominator, P in the io dtype -> shared memory (A operand of P.V):
       // row = 128 bytes of 64 keys, 16-byte chunks XOR-swizzled with the row number
-      const int b = j & 1;
+      const int b = (jg + j) & 1;
       const uint32_t prow = p_s0 + b * kPBytes + (uint32_t)row * 128u;
 #pragma unroll
       for (int c = 0; c < KT / 8; ++c) {
@@ -480,9 +526,10 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(pready0 + 8u * b);
-      if (j > 0 && !convert_pv(j - 1)) { ok = false; break; }
+      if (j > 0 && !convert_pv(jg + j - 1)) { ok = false; break; }
     }
-    if (ok && n_tiles > 0 && !convert_pv(n_tiles - 1)) ok = false;
+    if (ok && n_tiles > 0 && !convert_pv(jg + n_tiles - 1)) ok = false;
+    jg += n_tiles;
 
     // =============================== output ===========================================
     // KT weights per tile went through the fast add in this thread
@@ -516,6 +563,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         *reinterpret_cast<uint4*>(op + g8 * 8) = *reinterpret_cast<const uint4*>(out);
       }
+    }
     }
   }
 
@@ -624,8 +672,14 @@ int attention_tc(const AttnParams& p, int dtype, int max_query_len, int32_t* sta
   }
 
   constexpr int kSmem = kTcRows * 128 * 2 + kTcStages * 2 * kTcTileN * 128 * 2 + 2 * kTcRows * kTcTileN * 2 +
-                        8 * (1 + 2 * kTcStages + 10 + 1) + 16 + 2048 + 4096 + 1024;
-  dim3 grid((unsigned)(sh.num_q_blocks * p.num_kv_heads), (unsigned)p.num_reqs, 1);
+                        8 * (1 + 2 * kTcStages + 10 + 2) + 16 + 2048 + 4096 + 1024;
+  // persistent CTAs, one per SM (204 KB of shared memory each), walking the padded item list
+  int dev_now = 0, sms = 0;
+  cudaGetDevice(&dev_now);
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev_now) != cudaSuccess || sms < 1) sms = 148;
+  const int64_t total_items = (int64_t)sh.num_q_blocks * p.num_kv_heads * p.num_reqs;
+  if (total_items > 0x7fffffffLL) return FXPR_ERR_UNSUPPORTED;
+  dim3 grid((unsigned)std::min<int64_t>(total_items, sms), 1, 1);
 #define FXPR_TC_ATTN(TT)                                                                              \
   do {                                                                                                \
     auto k = attn_tc_prefill_kernel<TT, 128>;                                                         \
