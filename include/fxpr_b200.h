@@ -45,6 +45,7 @@ extern "C" {
 #define FXPR_GEMM_TILE_N256       64 /* force 128 x 256 output tiles (same bits) */
 #define FXPR_GEMM_TILE_N128       128 /* force 128 x 128 output tiles (same bits) */
 #define FXPR_GEMM_SILU_MUL        1024 /* B's columns are (gate_j, up_j) pairs; c is [M, N/2] = silu(gate) * up, computed from the GEMM outputs as the io dtype holds them (same bits as fxpr_gemm + fxpr_silu_mul_pairs); M <= 64 on the tensor-core decode route with c_int == NULL, else FXPR_ERR_UNSUPPORTED */
+#define FXPR_GEMM_WEIGHTS_STATIC  2048 /* the caller vouches that b was complete before this launch was enqueued behind its predecessor (model weights): the decode-shape kernel may then fetch its first weight tiles while the previous kernel of the stream is still running (programmatic dependent launch) */
 #define FXPR_GEMM_PAIR            512 /* two-SM kernel (gemm_tc_pair.cu): 256 x BN tiles on CTA pairs, tcgen05 cta_group::2; same bits, opt-in */
 
 /* ---- attention flags --------------------------------------------------- */

@@ -456,6 +456,7 @@ int gemm_tc(const GemmArgs& g, cudaStream_t s) {
   p.status = g.status;
   p.silu_mul = 0;
   p.best = nullptr; p.n_offset = 0;
+  p.w_static = (g.flags & FXPR_GEMM_WEIGHTS_STATIC) ? 1 : 0;
   const int k_tiles = (int)((g.K + g.k_tile - 1) / g.k_tile);
   p.split_k = g.split_k < 1 ? 1 : (g.split_k > k_tiles ? k_tiles : g.split_k);
   p.acc_scratch = nullptr; p.locks = nullptr;

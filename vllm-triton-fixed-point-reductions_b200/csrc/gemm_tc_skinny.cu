@@ -78,9 +78,12 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_co
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // barriers, tensor memory and descriptors are set up; from here on the kernel reads what
-  // earlier kernels of the stream wrote
-  pdl_wait();
+  // Barriers, tensor memory and descriptors are set up; from here on the kernel reads what
+  // earlier kernels of the stream wrote -- except, when the caller vouches for it
+  // (FXPR_GEMM_WEIGHTS_STATIC), the weights: the producer warp then requests the weight boxes of
+  // its first stages BEFORE it waits, so their HBM latency (~2.7 us cold) passes while the
+  // previous kernel finishes.
+  if (warp != 0) pdl_wait();
 
   const int tiles_n = p.tiles_n;                         // 128-column tiles; one row tile (M <= 64)
   const int items = tiles_n * p.split_k;
@@ -101,36 +104,60 @@ gemm_tc_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_co
     // ~260 clocks of the issuing thread), so super-stage j waits for the group barrier of
     // super-stage j - STAGES.
     int stage = 0; int wgrp = 0; uint32_t wphase = 0; int issued = 0;
-    for (int item = first_item; item < items; item += item_step) {
+    // boxes of super-stage ss of an item into shared-memory stage st: weights and/or activations
+    auto issue_boxes = [&](int item, int ss, int st, bool arm, bool weights, bool acts) {
       const int n0 = (item / p.split_k) * 128;
       const int ks = item % p.split_k;
       const int n_kt = (k_tiles_total - ks + p.split_k - 1) / p.split_k;
-      const int n_ss = pairs ? (n_kt + 1) >> 1 : n_kt;
+      const int ka = pairs ? (ks + (2 * ss) * p.split_k) * 64 : (ks + ss * p.split_k) * 128;
+      const int kb = pairs ? ka + p.split_k * 64 : ka + 64;
+      const bool two = pairs ? (2 * ss + 1 < n_kt) : true;
+      const uint32_t fb = full0 + 8u * st;
+      const uint32_t sw = smem_base + st * kSkSSBytes;
+      const uint32_t sx = sw + kSkWBytes;
+      if (lane == 0) {
+        if (arm) mbar_expect_tx(fb, two ? kSkSSBytes : kSkSSBytes / 2);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          if (h == 1 && !two) break;
+          const int kk = h ? kb : ka;
+          if (weights) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+              tma_load_2d(sw + h * (kSkWBytes / 2) + j * 8192, &tma_w, fb, wk ? kk : n0 + j * 64, wk ? n0 + j * 64 : kk);
+          }
+          if (acts) tma_load_2d(sx + h * (kSkXBytes / 2), &tma_x, fb, kk, 0);
+        }
+      }
+      __syncwarp();
+    };
+    auto n_ss_of = [&](int item) {
+      const int ks = item % p.split_k;
+      const int n_kt = (k_tiles_total - ks + p.split_k - 1) / p.split_k;
+      return pairs ? (n_kt + 1) >> 1 : n_kt;
+    };
+    // weights of the first item's first stages, then the dependency wait, then their activations
+    int early = 0;
+    if (p.w_static && first_item < items) {
+      early = min(STAGES, n_ss_of(first_item));
+      for (int ss = 0; ss < early; ++ss) issue_boxes(first_item, ss, ss, true, true, false);
+    }
+    pdl_wait();
+    for (int ss = 0; ss < early; ++ss) issue_boxes(first_item, ss, ss, false, false, true);
+    for (int item = first_item; item < items; item += item_step) {
+      const int n_ss = n_ss_of(item);
       for (int ss = 0; ss < n_ss; ++ss) {
-        const int ka = pairs ? (ks + (2 * ss) * p.split_k) * 64 : (ks + ss * p.split_k) * 128;
-        const int kb = pairs ? ka + p.split_k * 64 : ka + 64;
-        const bool two = pairs ? (2 * ss + 1 < n_kt) : true;
+        if (item == first_item && ss < early) {      // already requested above
+          ++issued;
+          if (++stage == STAGES) stage = 0;
+          continue;
+        }
         if (issued >= STAGES) {
           if (!__all_sync(0xffffffffu, mbar_wait(tfull0 + 8u * wgrp, wphase, abort_flag))) goto producer_done;
           if (++wgrp == ngroup) { wgrp = 0; wphase ^= 1; }
         }
         ++issued;
-        const uint32_t fb = full0 + 8u * stage;
-        const uint32_t sw = smem_base + stage * kSkSSBytes;
-        const uint32_t sx = sw + kSkWBytes;
-        if (lane == 0) {
-          mbar_expect_tx(fb, two ? kSkSSBytes : kSkSSBytes / 2);
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            if (h == 1 && !two) break;
-            const int kk = h ? kb : ka;
-#pragma unroll
-            for (int j = 0; j < 2; ++j)
-              tma_load_2d(sw + h * (kSkWBytes / 2) + j * 8192, &tma_w, fb, wk ? kk : n0 + j * 64, wk ? n0 + j * 64 : kk);
-            tma_load_2d(sx + h * (kSkXBytes / 2), &tma_x, fb, kk, 0);
-          }
-        }
-        __syncwarp();
+        issue_boxes(item, ss, stage, true, true, true);
         if (++stage == STAGES) stage = 0;
       }
     }

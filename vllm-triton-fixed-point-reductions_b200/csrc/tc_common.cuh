@@ -163,6 +163,7 @@ struct TcParams {
   int silu_mul;          // decode-shape kernel only: c[m, n / 2] = silu(out[m, n]) * out[m, n + 1], n even
   // decode-shape kernel only: best[m] = max over columns of argmax_key(out[m, n], n_offset + n)
   unsigned long long* best; unsigned int n_offset;
+  int w_static;          // decode-shape kernel: weight boxes may be requested before the dependency wait
 };
 
 // (value, column) packed so that an unsigned 64-bit maximum picks the largest value and, among

@@ -123,6 +123,20 @@ def overrides(*, gemm_k_tile=None, gemm_split_k=None, gemm_portable=None,
             setattr(_ovr, n, v)
 
 
+@contextlib.contextmanager
+def static_weights():
+    """Inside this block every GEMM's ``b`` operand is a model weight: complete long before the
+    launch and not written by any kernel in flight.  The decode-shape GEMM then requests its
+    first weight tiles before it waits for the previous kernel of the stream
+    (``FXPR_GEMM_WEIGHTS_STATIC``).  Results do not change."""
+    old = _ovr.gemm_flags
+    _ovr.gemm_flags = int(old) | nat.GEMM_WEIGHTS_STATIC
+    try:
+        yield
+    finally:
+        _ovr.gemm_flags = old
+
+
 # --------------------------------------------------------------------------
 # casts
 # --------------------------------------------------------------------------

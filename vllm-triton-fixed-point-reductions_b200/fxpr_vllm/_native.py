@@ -48,6 +48,7 @@ GEMM_NO_SKINNY = 8
 GEMM_NO_CLUSTER = 16
 GEMM_PAIR = 512
 GEMM_SILU_MUL = 1024
+GEMM_WEIGHTS_STATIC = 2048
 GEMM_TILE_N256 = 64
 GEMM_TILE_N128 = 128
 ATTN_CAUSAL = 1

@@ -27,7 +27,7 @@ import torch.distributed as dist
 
 from . import library_ops as ops
 from ._lib import (BLOCK_K_BY_DTYPE, argmax_from_keys, combine_argmax_keys, gemm_fxp_argmax, gemm_fxp_int_into,
-                   gemm_silu_mul, interleave_gate_up, rope_kv_write, silu_mul_pairs)
+                   gemm_silu_mul, interleave_gate_up, rope_kv_write, silu_mul_pairs, static_weights)
 from .config import get_runtime_config
 from .tp import check_shardable
 
@@ -233,6 +233,10 @@ class LlamaDecoder:
 
     # ------------------------------------------------------------------ forward
     def forward(self, tokens, seq_ids, pos, qsl, seq_lens, max_q: int, greedy_keys: bool = False):
+        with static_weights():               # every GEMM operand b below is a weight of the model
+            return self._forward(tokens, seq_ids, pos, qsl, seq_lens, max_q, greedy_keys)
+
+    def _forward(self, tokens, seq_ids, pos, qsl, seq_lens, max_q: int, greedy_keys: bool = False):
         """tokens/seq_ids/pos: [T] (flattened batch); returns the logits of each sequence's
         last token, [B, vocab] in the io dtype, identical on every rank.  With ``greedy_keys``
         the lm_head GEMM also leaves each row's arg-max key (no pass over the logits, and with

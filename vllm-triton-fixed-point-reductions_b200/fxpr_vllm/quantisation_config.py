@@ -50,7 +50,10 @@ class _FxpMethodBase(QuantizeMethodBase):
         self.fxp_frac_bits = rt.fxp_frac_bits
 
     def _matmul(self, layer: nn.Module, x: torch.Tensor, bias: torch.Tensor | None) -> torch.Tensor:
-        return gemm_fxp(x, layer.weight_native, bias, self.fxp_int_bits, self.fxp_frac_bits)
+        from ._lib import static_weights
+
+        with static_weights():               # weight_native is a loaded weight, never a kernel's fresh output
+            return gemm_fxp(x, layer.weight_native, bias, self.fxp_int_bits, self.fxp_frac_bits)
 
 
 class FixedPointLinearMethod(_FxpMethodBase):
