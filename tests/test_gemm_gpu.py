@@ -423,3 +423,24 @@ def test_gemm_argmax_keys_equal_argmax_of_the_logits(dtype, M, N, K):
     big = torch.randn(100, K, generator=g).to(dtype).cuda()      # more than 64 rows: two-kernel form
     lg2, k2 = L.gemm_fxp_argmax(big, b, None, 64, 16)
     assert torch.equal(L.argmax_from_keys(k2), lg2.argmax(dim=-1))
+
+
+@pytest.mark.parametrize("split", [0, 1, 4])
+def test_static_weights_promise_changes_no_bit(split):
+    """With FXPR_GEMM_WEIGHTS_STATIC the decode-shape kernel only moves its first weight requests
+    in front of the dependency wait; the outputs are the same, also back to back in one stream
+    with a kernel that writes the activations just before."""
+    from fxpr_vllm import _lib as L
+
+    g = torch.Generator().manual_seed(11)
+    w = (0.05 * torch.randn(2048, 1536, generator=g)).to(torch.bfloat16).cuda()
+    x0 = torch.randn(48, 2048, generator=g).cuda()
+    torch.cuda.synchronize()                                # the weights are complete, as the flag promises
+    kw = {} if split == 0 else {"gemm_split_k": split}
+    with L.overrides(gemm_k_tile=128, **kw):
+        wants = {sc: torch.ops.fxpr.gemm_fxp((x0 * sc).to(torch.bfloat16), w, None, 64, 16) for sc in (1.0, 0.5, 2.0)}
+        with L.static_weights():
+            for sc in (1.0, 0.5, 2.0):
+                x = (x0 * sc).to(torch.bfloat16)            # written by the kernel right before the GEMM
+                assert torch.equal(torch.ops.fxpr.gemm_fxp(x, w, None, 64, 16), wants[sc])
+        assert torch.equal(torch.ops.fxpr.gemm_fxp(x0.to(torch.bfloat16), w, None, 64, 16), wants[1.0])
