@@ -95,6 +95,25 @@ class DistGroup:
         dist.all_gather(out, parts[0].contiguous(), group=self.group)
         return torch.cat(out, dim=-1)
 
+    def reduce_scatter_rows(self, acc):
+        """Integer accumulators [T, H] of every rank -> this rank's T / size rows of their sum."""
+        rows = acc.shape[0] // self.size
+        r0 = dist.get_rank(self.group) * rows
+        if self.skip_collectives:
+            return acc[r0:r0 + rows].clone()
+        out = torch.empty((rows, acc.shape[1]), device=acc.device, dtype=acc.dtype)
+        dist.reduce_scatter_tensor(out, acc.contiguous(), op=dist.ReduceOp.SUM, group=self.group)
+        return out
+
+    def all_gather_rows(self, part):
+        """This rank's rows -> all rows, in rank order."""
+        out = torch.empty((part.shape[0] * self.size, part.shape[1]), device=part.device, dtype=part.dtype)
+        if self.skip_collectives:
+            out.view(self.size, *part.shape).copy_(part.unsqueeze(0).expand(self.size, *part.shape))
+            return out
+        dist.all_gather_into_tensor(out, part.contiguous(), group=self.group)
+        return out
+
     def all_gather_keys(self, parts):
         """Arg-max keys of this rank's vocab shard -> every shard's keys (8 bytes per row)."""
         if self.size == 1 or self.skip_collectives:
@@ -228,6 +247,16 @@ class LlamaDecoder:
             gemm_fxp_int_into(acts[0], weights[0], self.peer.acc[:rows], c.int_bits, c.frac_bits)
             return self.peer.reduce_norm(rows, norm_w, None, c.eps, c.frac_bits)
         accs = [ops.gemm_fxp_int(a, w, c.int_bits, c.frac_bits) for a, w in zip(acts, weights)]
+        if isinstance(self.group, DistGroup) and rows >= 1024 and rows % self.group.size == 0:
+            # Long batches (prefill): reduce-scatter by rows instead of all-reduce, residual add
+            # and norm on this rank's rows only, all-gather of the normalised rows in the io
+            # dtype.  The residual stays row-sharded for the whole forward pass (every exchange of
+            # a pass takes this branch, and a rank only ever reads its own rows of it), so per
+            # exchange 8 + 2 bytes per element cross the links instead of 16.  Same bits.
+            part = self.group.reduce_scatter_rows(accs[0])
+            r0 = self.group.local_ranks[0] * part.shape[0]
+            y = ops.rms_norm_fxp_from_int(part, residual[r0:r0 + part.shape[0]], norm_w, None, c.eps, c.frac_bits)
+            return self.group.all_gather_rows(y)
         accs = self.group.all_reduce_int(accs)
         return ops.rms_norm_fxp_from_int(accs[0], residual, norm_w, None, c.eps, c.frac_bits)
 
