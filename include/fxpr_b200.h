@@ -128,8 +128,11 @@ int fxpr_rms_norm_from_int(const void* acc, int int_bits, const void* bias,
  * reduces rows [r * ceil(rows / world), ...).  All ranks must issue the same sequence of calls.
  * Waits last at most timeout_cycles SM clocks (<= 0: about a second); when one runs out the
  * kernel writes FXPR_ERR_TIMEOUT to *status and stops touching peer memory; the buffers must
- * then be re-created.  int_bits 32 or 64; hidden a multiple of 4, at most 16384.
+ * then be re-created.  int_bits 32 or 64; hidden a multiple of 4, at most 16384.  flags:
+ * FXPR_TP_LOCAL_RESIDUAL -- the new residual rows are written to this rank's buffer only (for
+ * callers that keep the residual row-sharded: a rank only ever reads the residual of its own rows).
  */
+#define FXPR_TP_LOCAL_RESIDUAL 1
 int fxpr_tp_buffer_bytes(int64_t max_rows, int64_t hidden, int int_bits, int dtype,
                          int64_t* acc_offset, int64_t* residual_offset, int64_t* y_offset,
                          int64_t* flags_offset, int64_t* total);
@@ -141,7 +144,8 @@ int fxpr_tp_reduce_norm(const void* const* peer_bases, int world, int rank, void
                         int64_t acc_offset, int64_t residual_offset, int64_t y_offset,
                         int64_t flags_offset, int int_bits, const void* bias, const void* weight,
                         int dtype, int64_t rows, int64_t hidden, float eps, int gemm_frac_bits,
-                        int frac_bits, int64_t timeout_cycles, int32_t* status, void* stream);
+                        int frac_bits, int64_t timeout_cycles, int flags, int32_t* status,
+                        void* stream);
 
 /*
  * Row-wise log-softmax of a contiguous [rows, cols] matrix into fp32:

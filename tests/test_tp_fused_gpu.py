@@ -102,6 +102,20 @@ _WORKER = textwrap.dedent("""
             want = torch.ops.fxpr.rms_norm_fxp_from_int(tot, res, w, None, 1e-6, 16)
             got = pr.reduce_norm(n, w, None, 1e-6, 16)
             ok &= bool(torch.equal(got, want)) and bool(torch.equal(pr.residual[:n], res))
+    # row-sharded residual: a rank keeps only its own rows of its residual copy current
+    n = 64
+    res = res0.clone()
+    pr.residual[:n].copy_(res)
+    per = -(-n // world)
+    lo, hi = rank * per, min(n, (rank + 1) * per)
+    for it in range(3):
+        acc = (torch.randn(n, hidden, generator=gr) * 3 * 65536).to(torch.int64).to(dev)
+        pr.acc[:n].copy_(acc)
+        tot = acc.clone()
+        dist.all_reduce(tot)
+        want = torch.ops.fxpr.rms_norm_fxp_from_int(tot, res, w, None, 1e-6, 16)
+        got = pr.reduce_norm(n, w, None, 1e-6, 16, local_residual=True)
+        ok &= bool(torch.equal(got, want)) and bool(torch.equal(pr.residual[lo:hi], res[lo:hi]))
     # replayed from a CUDA graph: the call counter lives on the device
     pr.residual[:rows].copy_(res0)
     acc = (torch.randn(rows, hidden, generator=gr) * 3 * 65536).to(torch.int64).to(dev)

@@ -70,7 +70,7 @@ __global__ void __launch_bounds__(kTpThreads)
 tp_reduce_norm_kernel(const TpPeers peers, uint32_t* __restrict__ ctl, int world, int rank, int rows,
                       int rows_per_rank, int hidden, const T* __restrict__ bias, const T* __restrict__ w,
                       float eps, float gemm_inv_scale, float scale, float inv_scale, long long timeout,
-                      int32_t* status) {
+                      int32_t* status, int local_residual) {
   using UACC = typename std::conditional<sizeof(ACC) == 8, unsigned long long, uint32_t>::type;
   extern __shared__ __align__(16) float row_cache[];
   __shared__ long long red[32];
@@ -141,11 +141,12 @@ tp_reduce_norm_kernel(const TpPeers peers, uint32_t* __restrict__ ctl, int world
         if (p < world) {
           T* rp = reinterpret_cast<T*>(peers.residual[p]) + base + c;
           T* yp = reinterpret_cast<T*>(peers.y[p]) + base + c;
+          const bool res_too = !local_residual || p == rank;   // a row-sharded residual stays at home
           if (sizeof(T) == 2) {
-            *reinterpret_cast<uint2*>(rp) = *reinterpret_cast<const uint2*>(rv);
+            if (res_too) *reinterpret_cast<uint2*>(rp) = *reinterpret_cast<const uint2*>(rv);
             *reinterpret_cast<uint2*>(yp) = *reinterpret_cast<const uint2*>(yv);
           } else {
-            *reinterpret_cast<uint4*>(rp) = *reinterpret_cast<const uint4*>(rv);
+            if (res_too) *reinterpret_cast<uint4*>(rp) = *reinterpret_cast<const uint4*>(rv);
             *reinterpret_cast<uint4*>(yp) = *reinterpret_cast<const uint4*>(yv);
           }
         }
@@ -175,7 +176,7 @@ tp_reduce_norm_kernel(const TpPeers peers, uint32_t* __restrict__ ctl, int world
 template <typename T>
 static int launch_tp(const TpPeers& peers, void* ctl, int world, int rank, int int_bits, const void* bias,
                      const void* w, int64_t rows, int hidden, float eps, float gemm_inv, float scale, float inv,
-                     long long timeout, int32_t* status, cudaStream_t s) {
+                     long long timeout, int32_t* status, int local_residual, cudaStream_t s) {
   const int rows_per = (int)((rows + world - 1) / world);
   const int mine = (int)std::max<int64_t>(0, std::min<int64_t>(rows_per, rows - (int64_t)rank * rows_per));
   const unsigned grid = (unsigned)std::max(1, mine);
@@ -189,7 +190,7 @@ static int launch_tp(const TpPeers& peers, void* ctl, int world, int rank, int i
     }                                                                                                 \
     cudaError_t le = launch_pdl(k, dim3(grid), dim3(kTpThreads), smem, s, 1u, peers, (uint32_t*)ctl, world, rank, \
                                 (int)rows, rows_per, hidden, (const T*)bias, (const T*)w, eps, gemm_inv, scale,  \
-                                inv, timeout, status);                                                \
+                                inv, timeout, status, local_residual);                                \
     if (le != cudaSuccess) { set_last_error("tp_reduce_norm launch", le); return FXPR_ERR_CUDA; }     \
   } while (0)
   if (int_bits == 64) FXPR_TP_LAUNCH(long long);
@@ -267,7 +268,8 @@ extern "C" int fxpr_tp_reduce_norm(const void* const* peer_bases, int world, int
                                    int64_t acc_offset, int64_t residual_offset, int64_t y_offset,
                                    int64_t flags_offset, int int_bits, const void* bias, const void* weight,
                                    int dtype, int64_t rows, int64_t hidden, float eps, int gemm_frac_bits,
-                                   int frac_bits, int64_t timeout_cycles, int32_t* status, void* stream) {
+                                   int frac_bits, int64_t timeout_cycles, int flags, int32_t* status,
+                                   void* stream) {
   if (!peer_bases || !ctl || !weight || !status) return FXPR_ERR_BAD_ARG;
   if (world < 1 || world > kTpMaxWorld || rank < 0 || rank >= world) return FXPR_ERR_BAD_ARG;
   if (rows < 0 || hidden <= 0 || frac_bits < 0 || frac_bits >= 63 || gemm_frac_bits < 0 || gemm_frac_bits >= 63)
@@ -289,9 +291,9 @@ extern "C" int fxpr_tp_reduce_norm(const void* const* peer_bases, int world, int
   const float gemm_inv = 1.0f / (float)(1ull << gemm_frac_bits);
   cudaStream_t s = (cudaStream_t)stream;
   switch (dtype) {
-    case FXPR_F32: return launch_tp<float>(peers, ctl, world, rank, int_bits, bias, weight, rows, (int)hidden, eps, gemm_inv, scale, inv, timeout_cycles, status, s);
-    case FXPR_F16: return launch_tp<__half>(peers, ctl, world, rank, int_bits, bias, weight, rows, (int)hidden, eps, gemm_inv, scale, inv, timeout_cycles, status, s);
-    case FXPR_BF16: return launch_tp<__nv_bfloat16>(peers, ctl, world, rank, int_bits, bias, weight, rows, (int)hidden, eps, gemm_inv, scale, inv, timeout_cycles, status, s);
+    case FXPR_F32: return launch_tp<float>(peers, ctl, world, rank, int_bits, bias, weight, rows, (int)hidden, eps, gemm_inv, scale, inv, timeout_cycles, status, (flags & FXPR_TP_LOCAL_RESIDUAL) ? 1 : 0, s);
+    case FXPR_F16: return launch_tp<__half>(peers, ctl, world, rank, int_bits, bias, weight, rows, (int)hidden, eps, gemm_inv, scale, inv, timeout_cycles, status, (flags & FXPR_TP_LOCAL_RESIDUAL) ? 1 : 0, s);
+    case FXPR_BF16: return launch_tp<__nv_bfloat16>(peers, ctl, world, rank, int_bits, bias, weight, rows, (int)hidden, eps, gemm_inv, scale, inv, timeout_cycles, status, (flags & FXPR_TP_LOCAL_RESIDUAL) ? 1 : 0, s);
   }
   return FXPR_ERR_UNSUPPORTED;
 }

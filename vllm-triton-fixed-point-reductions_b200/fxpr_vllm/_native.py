@@ -49,6 +49,7 @@ GEMM_NO_CLUSTER = 16
 GEMM_PAIR = 512
 GEMM_SILU_MUL = 1024
 GEMM_WEIGHTS_STATIC = 2048
+TP_LOCAL_RESIDUAL = 1
 GEMM_TILE_N256 = 64
 GEMM_TILE_N128 = 128
 ATTN_CAUSAL = 1
@@ -75,7 +76,7 @@ SIGNATURES = {
     "fxpr_tp_close": (_i, [_vp]),
     "fxpr_tp_free": (_i, [_vp]),
     "fxpr_tp_reduce_norm": (_i, [_vp, _i, _i, _vp, _i64, _i64, _i64, _i64, _i, _vp, _vp, _i, _i64, _i64, _f,
-                                 _i, _i, _i64, _vp, _vp]),
+                                 _i, _i, _i64, _i, _vp, _vp]),
     "fxpr_rope_kv_write": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _i64, _i, _i, _i, _i,
                                 _i64, _i64, _i64, _i64, _vp]),
     "fxpr_silu_mul": (_i, [_vp, _i, _vp, _i64, _i64, _vp]),

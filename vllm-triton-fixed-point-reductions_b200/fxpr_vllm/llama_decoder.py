@@ -245,7 +245,8 @@ class LlamaDecoder:
         if self.peer is not None and rows <= self.peer.max_rows and not self.group.skip_collectives:
             # `residual` is the peer buffer's residual window (see forward)
             gemm_fxp_int_into(acts[0], weights[0], self.peer.acc[:rows], c.int_bits, c.frac_bits)
-            return self.peer.reduce_norm(rows, norm_w, None, c.eps, c.frac_bits)
+            # the residual only ever comes back into this call: each rank keeps its own rows current
+            return self.peer.reduce_norm(rows, norm_w, None, c.eps, c.frac_bits, local_residual=True)
         accs = [ops.gemm_fxp_int(a, w, c.int_bits, c.frac_bits) for a, w in zip(acts, weights)]
         if isinstance(self.group, DistGroup) and rows >= 1024 and rows % self.group.size == 0:
             # Long batches (prefill): reduce-scatter by rows instead of all-reduce, residual add

@@ -124,9 +124,11 @@ class PeerReduceNorm:
         return ptr.value, bytes(handle)
 
     def reduce_norm(self, rows: int, weight: torch.Tensor, bias: torch.Tensor | None, eps: float,
-                    gemm_frac_bits: int) -> torch.Tensor:
+                    gemm_frac_bits: int, local_residual: bool = False) -> torch.Tensor:
         """Sum ``acc[:rows]`` over the ranks, update ``residual[:rows]`` on every rank and
-        return the normalised rows (a view of ``y``)."""
+        return the normalised rows (a view of ``y``).  With ``local_residual`` a rank updates only
+        its own rows of its own residual copy (rows ``[rank * ceil(rows / world), ...)``): enough
+        when the residual is only ever fed back into this call, and less traffic."""
         if not 0 <= rows <= self.max_rows:
             raise ValueError(f"rows={rows} exceeds the buffer's {self.max_rows}")
         if weight.dtype != self.io_dtype or weight.numel() != self.hidden:
@@ -138,6 +140,7 @@ class PeerReduceNorm:
                 self.y_off, self.flags_off, self.int_bits, nat.ptr(b), weight.contiguous().data_ptr(),
                 nat.DTYPE_CODE[self.io_dtype], rows, self.hidden, float(eps), int(gemm_frac_bits),
                 get_runtime_config().fxp_frac_bits, self.timeout_cycles,
+                nat.TP_LOCAL_RESIDUAL if local_residual else 0,
                 _status_word(self.device).data_ptr(), nat.stream_ptr(self.device))
         nat.check(st, "tp_reduce_norm")
         return self.y[:rows]
